@@ -39,7 +39,7 @@ class LayerSpec:
     """
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]      # None: the layer has no feed-forward (its block must know)
     norms: Dict[str, PartSpec]
 
 
@@ -85,6 +85,7 @@ class ModelPlan:
                 if self.schedule[run.kv_from].kv_from is not None:
                     raise ConfigError(f"run {i} reads the cache of run {run.kv_from}, which owns none")
         for layer in self.layers:
-            pos = layer.mixer.params.get("position")
-            if pos is not None and pos not in self.positions:
-                raise ConfigError(f"mixer names position encoding {pos!r}, the plan has {sorted(self.positions)}")
+            named = [layer.mixer.params.get("position")] + [m["params"].get("position") for m in layer.mixer.params.get("mixers", ())]
+            for pos in named:
+                if pos is not None and pos not in self.positions:
+                    raise ConfigError(f"mixer names position encoding {pos!r}, the plan has {sorted(self.positions)}")

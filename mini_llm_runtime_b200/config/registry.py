@@ -60,8 +60,10 @@ def read_config_json(model_dir: str) -> dict:
 
 
 def config_from_dict(raw: dict):
-    """Pick the config class by `architectures[0]` and parse."""
+    """Pick the config class by `architectures[0]` (or by `architecture`, a single name) and parse."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError(f"config.json needs a non-empty 'architectures' list; known: {known_architectures()}")
     config_cls, _ = architecture(archs[0])

@@ -781,9 +781,13 @@ int mlr_model_step(void* handle, int n, const int32_t* slots, const int32_t* cou
     }
     if (rc == 0 && graphed) {
         auto found = m.graphs.find(key);
+        bool done = false;
         if (found == m.graphs.end()) {
-            // Warm-up outside the capture (the step is idempotent: it rewrites the same cache rows), then the capture.
+            // This step's work runs launch by launch (which also warms the kernels up), then the same launches are
+            // captured for the steps to come.  The graph is not launched for this step: a mixer that keeps a state
+            // per request advances it with every run, so a step's work must run exactly once.
             rc = run_program(*program, vars);
+            done = true;
             if (rc == 0 && m.capture_stream == nullptr && cudaStreamCreateWithFlags(&m.capture_stream, cudaStreamNonBlocking) != cudaSuccess)
                 rc = fail(kStepFailed, "cannot create the capture stream");
             GraphEntry entry;
@@ -824,7 +828,8 @@ int mlr_model_step(void* handle, int n, const int32_t* slots, const int32_t* cou
                 if (entry.graph) cudaGraphDestroy(entry.graph);
             }
         }
-        if (rc == 0) {
+        if (done) info->graphed = 0;       // this step's launches were ordinary ones
+        if (rc == 0 && !done) {
             const cudaError_t e = cudaGraphLaunch(found->second.exec, stream);
             if (e != cudaSuccess) rc = fail(kStepFailed, "launching the graph failed: %s", cudaGetErrorString(e));
             else g_launches += found->second.launches;

@@ -436,6 +436,25 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     }
 }
 
+// Gated activation with biases: out = act(gate + b_gate) * (up + b_up), gate in the first `inter` columns of a row
+// and up in the next `inter`; act is SiLU (0) or the tanh form of GELU (1).  Biases are float32, may be null.
+template <typename T>
+__global__ void gated_bias_kernel(const T* gate_up, int ld, const float* bias_gate, const float* bias_up, T* out, int ld_out,
+                                  int rows, int inter, int activation) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    const size_t total = static_cast<size_t>(rows) * inter;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / inter, c = i - r * inter;
+        const float g = mlr_load(gate_up, r * ld + c) + (bias_gate ? bias_gate[c] : 0.0f);
+        const float u = mlr_load(gate_up, r * ld + inter + c) + (bias_up ? bias_up[c] : 0.0f);
+        const float a = activation == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                        : g / (1.0f + expf(-g));
+        mlr_store(out, r * ld_out + c, a * u);
+    }
+}
+
 template <typename T>
 __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inter, int block) {
     mlr_grid_dependents_may_start();
@@ -625,6 +644,21 @@ MLR_API int mlr_swiglu(const void* gate_up, void* out, int act_bf16, int rows, i
     else
         mlr_launch((swiglu_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), static_cast<float*>(out), rows, inter, block);
     return mlr_launched("swiglu");
+}
+
+MLR_API int mlr_gated_bias(const void* gate_up, int ld, const float* bias_gate, const float* bias_up, void* out, int ld_out,
+                           int act_bf16, int rows, int inter, int activation, cudaStream_t stream) {
+    MLR_REQUIRE(rows >= 0 && inter > 0 && ld >= 2 * inter && ld_out >= inter, "gated_bias: bad sizes rows=%d inter=%d", rows, inter);
+    MLR_REQUIRE(activation == 0 || activation == 1, "gated_bias: unknown activation %d", activation);
+    if (rows == 0) return 0;
+    const int blocks = mlr_grid_stride_blocks(static_cast<size_t>(rows) * inter / 1024 + 1, 16);
+    if (act_bf16)
+        mlr_launch((gated_bias_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate_up), ld,
+                   bias_gate, bias_up, static_cast<__nv_bfloat16*>(out), ld_out, rows, inter, activation);
+    else
+        mlr_launch((gated_bias_kernel<float>), dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(gate_up), ld, bias_gate,
+                   bias_up, static_cast<float*>(out), ld_out, rows, inter, activation);
+    return mlr_launched("gated_bias");
 }
 
 // The same from `slices` float32 partial sums of the stacked product [slices][rows][2 * inter].

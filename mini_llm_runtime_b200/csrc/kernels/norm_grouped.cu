@@ -1,0 +1,94 @@
+// RMS norm in groups, on the float32 residual stream, as the two halves of a block that norms
+// both what goes into a sub-layer and what comes out of it:
+//
+//   if delta:  h[row] += groupnorm(delta[row] + bias) * w_post      (the sub-layer's result, normed, joins the stream;
+//                                                                   with norm_delta = 0 it joins as it is)
+//   if out:    out[r]  = groupnorm(h[row]) * w_pre                  (the next sub-layer's input)
+//
+// groupnorm(x): x in `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps).
+// groups = 1 is the ordinary RMS norm.  row = rows[r] when an index list is given (the wanted rows
+// before the head), else r.  One block per row; the row is staged in shared memory, each warp
+// sums whole groups in a fixed order, so a row's result depends on nothing but the row.
+// All arithmetic is float32; `out` is float32 or bfloat16; weights and the bias are float32.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ void group_inverse_rms(const float* vals, float* inv, int width, int groups, float eps) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int part = width / groups;
+    for (int g = warp; g < groups; g += warps) {
+        const float* x = vals + static_cast<size_t>(g) * part;
+        float sum = 0.0f;
+        for (int i = lane; i < part; i += 32) sum = fmaf(x[i], x[i], sum);
+        sum = mlr_warp_sum(sum);
+        if (lane == 0) inv[g] = 1.0f / sqrtf(sum / static_cast<float>(part) + eps);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const float* delta, int ld_delta, const float* bias,
+                                                                 const float* w_post, const float* w_pre, T* out, int ld_out,
+                                                                 const int* rows, int width, int groups, float eps, int norm_delta) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* vals = reinterpret_cast<float*>(smem);
+    float* inv = vals + width;
+    const int row = rows ? rows[blockIdx.x] : blockIdx.x;
+    const int part = width / groups;
+    float* hrow = h + static_cast<size_t>(row) * width;
+    if (delta) {
+        const float* d = delta + static_cast<size_t>(row) * ld_delta;
+        for (int i = threadIdx.x; i < width; i += kThreads) vals[i] = d[i] + (bias ? bias[i] : 0.0f);
+        __syncthreads();
+        if (norm_delta) group_inverse_rms(vals, inv, width, groups, eps);
+        __syncthreads();
+        for (int i = threadIdx.x; i < width; i += kThreads) {
+            const float normed = norm_delta ? vals[i] * inv[i / part] : vals[i];
+            const float sum = hrow[i] + (w_post ? normed * w_post[i] : normed);
+            hrow[i] = sum;
+            vals[i] = sum;
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += kThreads) vals[i] = hrow[i];
+    }
+    if (!out) return;
+    __syncthreads();
+    group_inverse_rms(vals, inv, width, groups, eps);
+    __syncthreads();
+    T* o = out + static_cast<size_t>(blockIdx.x) * ld_out;
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+        const float normed = vals[i] * inv[i / part];
+        mlr_store(o, i, w_pre ? normed * w_pre[i] : normed);
+    }
+}
+
+}  // namespace
+
+MLR_API int mlr_group_rmsnorm(float* h, const float* delta, int ld_delta, const float* bias, const float* w_post,
+                              const float* w_pre, void* out, int ld_out, int out_bf16, const int* rows, int count, int width,
+                              int groups, float eps, int norm_delta, cudaStream_t stream) {
+    MLR_REQUIRE(count >= 0 && width > 0 && groups > 0 && width % groups == 0,
+                "group_rmsnorm: width %d cannot be cut into %d equal groups", width, groups);
+    MLR_REQUIRE(eps >= 0.0f, "group_rmsnorm: eps must not be negative");
+    MLR_REQUIRE(h && (delta || out), "group_rmsnorm: nothing to do");
+    MLR_REQUIRE(!delta || (ld_delta >= width && !rows), "group_rmsnorm: a contribution is added for all rows, with a row stride >= width");
+    MLR_REQUIRE(!out || ld_out >= width, "group_rmsnorm: the output's row stride is smaller than the width");
+    if (count == 0) return 0;
+    const size_t shared = sizeof(float) * (static_cast<size_t>(width) + groups);
+    MLR_REQUIRE(shared <= 200 * 1024, "group_rmsnorm: a row of %d values does not fit shared memory", width);
+    if (shared > 48 * 1024) {
+        cudaFuncSetAttribute(group_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        cudaFuncSetAttribute(group_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+    }
+    if (out_bf16)
+        mlr_launch((group_rmsnorm_kernel<__nv_bfloat16>), dim3(count), dim3(kThreads), shared, stream, h, delta, ld_delta, bias, w_post,
+                   w_pre, static_cast<__nv_bfloat16*>(out), ld_out, rows, width, groups, eps, norm_delta);
+    else
+        mlr_launch((group_rmsnorm_kernel<float>), dim3(count), dim3(kThreads), shared, stream, h, delta, ld_delta, bias, w_post, w_pre,
+                   static_cast<float*>(out), ld_out, rows, width, groups, eps, norm_delta);
+    return mlr_launched("group_rmsnorm");
+}

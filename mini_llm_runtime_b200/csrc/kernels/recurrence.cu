@@ -1,0 +1,351 @@
+// Mixers that keep a matrix per head and request instead of keys and values: a state S [dim, vdim],
+// float32, that every token updates and reads.  One kernel serves the family; what varies between
+// designs is a description in host memory (`RecurrenceSpec`):
+//
+//   preparation of q and k (float32, from the projections' output):
+//       rotate:  the first rot_dims values turned by position * freq[i] (value i paired with i + rot_dims/2)
+//       unit:    x / sqrt(sum(x^2) + unit_eps)
+//     then q *= q_mult, k *= k_mult
+//   rule, token by token:
+//       decay:   S <- decay[head] S + k v^T;                            o = S^T q       (retention)
+//       delta:   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;      o = S^T q       (gated delta rule)
+//                with g = exp(-exp(a_log[head]) softplus(a + dt_bias[head])), beta = sigmoid(b), from two more
+//                columns of the projections' output per head
+//   (q, k, v come from one buffer, `proj`; a, b and the gate from another, `side`, which may be the same)
+//   read-out:    o / sqrt(mean(o^2) + eps) per head, times a weight [vdim] (optional), times silu(gate)
+//                or sigmoid(gate) (optional), times a constant
+//
+// The columns of S are independent of one another in both rules, so a warp owns a few columns (lanes
+// split `dim`), and one block owns one (request, head): it prepares a batch of tokens in shared memory,
+// its warps walk the batch token by token, and the block norms and gates the batch's outputs.  The
+// state is read at the start and written at the end; a new request's state is zero (the caller zeroes
+// the slot).  Everything but the loads of the projections and the store of the result is float32.
+//
+// `mlr_short_conv` is the causal convolution over time per channel that precedes such a mixer in some
+// designs (taps [channels, n], the last tap is the current token's; silu after it), with the last n-1
+// inputs of every request kept as state; `mlr_short_conv_state` moves that state on after a step.
+#include "common.cuh"
+
+struct RecurrenceSpec {
+    const float* freq;         // [rot_dims / 2] or null
+    const float* decay;        // [heads] (rule 0)
+    const float* a_log;        // [heads] (rule 1)
+    const float* dt_bias;      // [heads] (rule 1)
+    const float* out_weight;   // [vdim] or null
+    int heads, qk_heads, dim, vdim;
+    int prep;                  // 0 none, 1 rotate, 2 unit
+    int rot_dims;
+    int rule;                  // 0 decay, 1 delta
+    int gate_kind;             // 0 none, 1 sigmoid, 2 silu
+    int col_q, col_k, col_v;           // first columns of q, k, v in `proj`
+    int col_a, col_b, col_gate;        // first columns of the rule's two inputs and of the gate in `side`
+    float q_mult, k_mult, unit_eps, eps, out_scale;
+};
+
+namespace {
+
+__device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+template <typename T, int R, int COLS>
+__global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, int ld, const T* side, int ld_side, T* out, int ld_out, float* state,
+                                                                  long long state_stride, const int* segment_info, RecurrenceSpec s,
+                                                                  int batch) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* qs = reinterpret_cast<float*>(smem);          // [batch][dim]
+    float* ks = qs + static_cast<size_t>(batch) * s.dim; // [batch][dim]
+    float* vs = ks + static_cast<size_t>(batch) * s.dim; // [batch][vdim]
+    float* os = vs + static_cast<size_t>(batch) * s.vdim;  // [batch][vdim]
+    float* gs = os + static_cast<size_t>(batch) * s.vdim;  // [batch]
+    float* bs = gs + batch;                                 // [batch]
+
+    const int segment = blockIdx.x, head = blockIdx.y;
+    const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1];
+    const int start = segment_info[4 * segment + 2], slot = segment_info[4 * segment + 3];
+    const int qk_head = head / (s.heads / s.qk_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int threads = blockDim.x;
+    const int col0 = warp * COLS;
+
+    float S[COLS][R];
+    float* my_state = state + static_cast<size_t>(slot) * state_stride + (static_cast<size_t>(head) * s.vdim) * s.dim;
+#pragma unroll
+    for (int c = 0; c < COLS; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = lane + 32 * r;
+            S[c][r] = (col0 + c < s.vdim && d < s.dim) ? my_state[static_cast<size_t>(col0 + c) * s.dim + d] : 0.0f;
+        }
+    const float decay = s.rule == 0 ? s.decay[head] : 1.0f;
+    const int half = s.rot_dims / 2;
+
+    for (int base = 0; base < count; base += batch) {
+        const int n = min(batch, count - base);
+        // ---- prepare the batch: q, k, v (and the gates of the rule) as float32
+        for (int i = threadIdx.x; i < n * s.dim; i += threads) {
+            const int t = i / s.dim, c = i % s.dim;
+            const T* row = proj + static_cast<size_t>(first + base + t) * ld;
+            qs[i] = mlr_load(row, s.col_q + qk_head * s.dim + c);
+            ks[i] = mlr_load(row, s.col_k + qk_head * s.dim + c);
+        }
+        for (int i = threadIdx.x; i < n * s.vdim; i += threads) {
+            const int t = i / s.vdim, c = i % s.vdim;
+            vs[i] = mlr_load(proj + static_cast<size_t>(first + base + t) * ld, s.col_v + head * s.vdim + c);
+        }
+        if (s.rule == 1 && threadIdx.x < n) {
+            const T* row = side + static_cast<size_t>(first + base + threadIdx.x) * ld_side;
+            const float a = mlr_load(row, s.col_a + head), b = mlr_load(row, s.col_b + head);
+            gs[threadIdx.x] = expf(-expf(s.a_log[head]) * softplus(a + s.dt_bias[head]));
+            bs[threadIdx.x] = 1.0f / (1.0f + expf(-b));
+        }
+        __syncthreads();
+        if (s.prep == 1) {
+            for (int i = threadIdx.x; i < n * half; i += threads) {
+                const int t = i / half, c = i % half;
+                float sn, cs;
+                sincosf(static_cast<float>(start + base + t) * s.freq[c], &sn, &cs);
+                float* x = qs + static_cast<size_t>(t) * s.dim;
+                float u = x[c], v = x[c + half];
+                x[c] = u * cs - v * sn;
+                x[c + half] = v * cs + u * sn;
+                x = ks + static_cast<size_t>(t) * s.dim;
+                u = x[c], v = x[c + half];
+                x[c] = u * cs - v * sn;
+                x[c + half] = v * cs + u * sn;
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < n * s.dim; i += threads) {
+                qs[i] *= s.q_mult;
+                ks[i] *= s.k_mult;
+            }
+        } else if (s.prep == 2) {
+            for (int vec = warp; vec < 2 * n; vec += warps) {
+                float* x = (vec < n ? qs : ks) + static_cast<size_t>(vec < n ? vec : vec - n) * s.dim;
+                float sum = 0.0f;
+                for (int c = lane; c < s.dim; c += 32) sum = fmaf(x[c], x[c], sum);
+                const float inv = 1.0f / sqrtf(mlr_warp_sum(sum) + s.unit_eps);
+                const float mult = vec < n ? s.q_mult : s.k_mult;
+                for (int c = lane; c < s.dim; c += 32) x[c] = x[c] * inv * mult;
+            }
+        } else {
+            for (int i = threadIdx.x; i < n * s.dim; i += threads) {
+                qs[i] *= s.q_mult;
+                ks[i] *= s.k_mult;
+            }
+        }
+        __syncthreads();
+        // ---- the recurrence: this warp's columns, token by token
+        if (col0 < s.vdim) {
+            for (int t = 0; t < n; ++t) {
+                float kk[R], qq[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int d = lane + 32 * r;
+                    kk[r] = d < s.dim ? ks[static_cast<size_t>(t) * s.dim + d] : 0.0f;
+                    qq[r] = d < s.dim ? qs[static_cast<size_t>(t) * s.dim + d] : 0.0f;
+                }
+                float o[COLS];
+                if (s.rule == 0) {
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c) {
+                        const float v = col0 + c < s.vdim ? vs[static_cast<size_t>(t) * s.vdim + col0 + c] : 0.0f;
+                        float dot = 0.0f;
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            S[c][r] = fmaf(decay, S[c][r], kk[r] * v);
+                            dot = fmaf(S[c][r], qq[r], dot);
+                        }
+                        o[c] = dot;
+                    }
+                } else {
+                    const float g = gs[t], beta = bs[t];
+                    float dotk[COLS];
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c) {
+                        float dot = 0.0f;
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            S[c][r] *= g;
+                            dot = fmaf(S[c][r], kk[r], dot);
+                        }
+                        dotk[c] = dot;
+                    }
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c) dotk[c] = mlr_warp_sum(dotk[c]);
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c) {
+                        const float v = col0 + c < s.vdim ? vs[static_cast<size_t>(t) * s.vdim + col0 + c] : 0.0f;
+                        const float u = beta * (v - dotk[c]);
+                        float dot = 0.0f;
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            S[c][r] = fmaf(kk[r], u, S[c][r]);
+                            dot = fmaf(S[c][r], qq[r], dot);
+                        }
+                        o[c] = dot;
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < COLS; ++c) o[c] = mlr_warp_sum(o[c]);
+                if (lane == 0) {
+#pragma unroll
+                    for (int c = 0; c < COLS; ++c)
+                        if (col0 + c < s.vdim) os[static_cast<size_t>(t) * s.vdim + col0 + c] = o[c];
+                }
+            }
+        }
+        __syncthreads();
+        // ---- read-out of the batch: norm per head, weight, gate
+        for (int t = warp; t < n; t += warps) {
+            const float* o = os + static_cast<size_t>(t) * s.vdim;
+            float inv = 1.0f;
+            if (s.eps >= 0.0f) {
+                float sum = 0.0f;
+                for (int c = lane; c < s.vdim; c += 32) sum = fmaf(o[c], o[c], sum);
+                inv = 1.0f / sqrtf(mlr_warp_sum(sum) / static_cast<float>(s.vdim) + s.eps);
+            }
+            const T* prow = side + static_cast<size_t>(first + base + t) * ld_side;
+            T* orow = out + static_cast<size_t>(first + base + t) * ld_out + static_cast<size_t>(head) * s.vdim;
+            for (int c = lane; c < s.vdim; c += 32) {
+                float value = o[c] * inv;
+                if (s.out_weight) value *= s.out_weight[c];
+                if (s.gate_kind) {
+                    const float g = mlr_load(prow, s.col_gate + head * s.vdim + c);
+                    const float sig = 1.0f / (1.0f + expf(-g));
+                    value *= s.gate_kind == 2 ? g * sig : sig;
+                }
+                mlr_store(orow, c, value * s.out_scale);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int c = 0; c < COLS; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = lane + 32 * r;
+            if (col0 + c < s.vdim && d < s.dim) my_state[static_cast<size_t>(col0 + c) * s.dim + d] = S[c][r];
+        }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_kernel(const T* in, int ld_in, T* out, int ld_out, int channels, int taps,
+                                                         const float* weights, const float* state, long long state_stride,
+                                                         const int* segment_info, const int* segment_of_row) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    const int row = blockIdx.x;
+    const int segment = segment_of_row[row];
+    const int first = segment_info[4 * segment], slot = segment_info[4 * segment + 3];
+    const int j = row - first;
+    const float* old = state + static_cast<size_t>(slot) * state_stride;
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        float y = 0.0f;
+        for (int i = 0; i < taps; ++i) {
+            const int m = j - (taps - 1) + i;      // the input this tap sees, counted from the step's first token
+            const float x = m >= 0 ? mlr_load(in + static_cast<size_t>(first + m) * ld_in, c)
+                                   : old[static_cast<size_t>(taps - 1 + m) * channels + c];
+            y = fmaf(weights[static_cast<size_t>(c) * taps + i], x, y);
+        }
+        mlr_store(out + static_cast<size_t>(row) * ld_out, c, y / (1.0f + expf(-y)));
+    }
+}
+
+constexpr int kMaxTaps = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_state_kernel(const T* in, int ld_in, int channels, int taps, float* state,
+                                                               long long state_stride, const int* segment_info) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    const int segment = blockIdx.x;
+    const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], slot = segment_info[4 * segment + 3];
+    float* mine = state + static_cast<size_t>(slot) * state_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+        float kept[kMaxTaps];
+        for (int i = 0; i < taps - 1; ++i) kept[i] = mine[static_cast<size_t>(i) * channels + c];
+        for (int i = 0; i < taps - 1; ++i) {
+            const int m = count - (taps - 1) + i;
+            mine[static_cast<size_t>(i) * channels + c] =
+                m >= 0 ? mlr_load(in + static_cast<size_t>(first + m) * ld_in, c) : kept[taps - 1 + m];
+        }
+    }
+}
+
+}  // namespace
+
+MLR_API int mlr_linear_recurrence(const RecurrenceSpec* spec, const void* proj, int ld, const void* side, int ld_side, int act_bf16, void* out, int ld_out,
+                                  float* state, long long state_stride, const int* segment_info, int n_segments, int* status,
+                                  cudaStream_t stream) {
+    (void)status;
+    MLR_REQUIRE(spec, "linear_recurrence: no description");
+    const RecurrenceSpec& s = *spec;
+    MLR_REQUIRE(s.heads > 0 && s.qk_heads > 0 && s.heads % s.qk_heads == 0 && s.heads <= 65535,
+                "linear_recurrence: %d heads cannot share %d q/k heads", s.heads, s.qk_heads);
+    MLR_REQUIRE(s.dim >= 1 && s.dim <= 256 && s.vdim >= 1 && s.vdim <= 256 && !(s.dim > 128 && s.vdim > 128),
+                "linear_recurrence: a state of %d x %d per head is more than a block's registers hold (256 x 128 or 128 x 256)", s.dim, s.vdim);
+    MLR_REQUIRE(s.prep != 1 || (s.rot_dims >= 0 && s.rot_dims % 2 == 0 && s.rot_dims <= s.dim && (s.rot_dims == 0 || s.freq)),
+                "linear_recurrence: %d rotated values do not fit a head of %d", s.rot_dims, s.dim);
+    MLR_REQUIRE(s.rule == 0 ? s.decay != nullptr : (s.rule == 1 && s.a_log && s.dt_bias), "linear_recurrence: the rule's constants are missing");
+    MLR_REQUIRE(n_segments >= 0 && state && proj && side && out, "linear_recurrence: bad arguments");
+    if (n_segments == 0) return 0;
+    const int cols = s.vdim > 128 ? 8 : 4;
+    const int warps = (s.vdim + cols - 1) / cols;
+    const int regs = s.dim <= 32 ? 1 : s.dim <= 64 ? 2 : s.dim <= 128 ? 4 : 8;
+    const size_t per_token = sizeof(float) * (2 * static_cast<size_t>(s.dim) + 2 * s.vdim + 2);
+    int batch = static_cast<int>((40 * 1024) / per_token);
+    batch = batch < 1 ? 1 : (batch > 32 ? 32 : batch);
+    const size_t shared = per_token * batch;
+    const dim3 grid(n_segments, s.heads);
+#define MLR_GO(T, R, C)                                                                                                     \
+    mlr_launch((linear_recurrence_kernel<T, R, C>), dim3(grid), dim3(warps * 32), shared, stream, static_cast<const T*>(proj), ld, static_cast<const T*>(side), ld_side, \
+               static_cast<T*>(out), ld_out, state, state_stride, segment_info, s, batch)
+#define MLR_PICK(T)                                              \
+    do {                                                         \
+        if (cols == 4) {                                         \
+            if (regs == 1) MLR_GO(T, 1, 4);                      \
+            else if (regs == 2) MLR_GO(T, 2, 4);                 \
+            else if (regs == 4) MLR_GO(T, 4, 4);                 \
+            else MLR_GO(T, 8, 4);                                \
+        } else {                                                 \
+            if (regs == 1) MLR_GO(T, 1, 8);                      \
+            else if (regs == 2) MLR_GO(T, 2, 8);                 \
+            else MLR_GO(T, 4, 8);                                \
+        }                                                        \
+    } while (0)
+    if (act_bf16) MLR_PICK(__nv_bfloat16);
+    else MLR_PICK(float);
+#undef MLR_PICK
+#undef MLR_GO
+    return mlr_launched("linear_recurrence");
+}
+
+MLR_API int mlr_short_conv(const void* in, int ld_in, void* out, int ld_out, int act_bf16, int channels, int taps,
+                           const float* weights, const float* state, long long state_stride, const int* segment_info,
+                           const int* segment_of_row, int rows, cudaStream_t stream) {
+    MLR_REQUIRE(channels > 0 && taps >= 1 && taps <= kMaxTaps, "short_conv: %d taps are outside [1, %d]", taps, kMaxTaps);
+    MLR_REQUIRE(ld_in >= channels && ld_out >= channels && (taps == 1 || state), "short_conv: bad strides or no state");
+    if (rows <= 0) return 0;
+    if (act_bf16)
+        mlr_launch((short_conv_kernel<__nv_bfloat16>), dim3(rows), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), ld_in,
+                   static_cast<__nv_bfloat16*>(out), ld_out, channels, taps, weights, state, state_stride, segment_info, segment_of_row);
+    else
+        mlr_launch((short_conv_kernel<float>), dim3(rows), dim3(256), 0, stream, static_cast<const float*>(in), ld_in,
+                   static_cast<float*>(out), ld_out, channels, taps, weights, state, state_stride, segment_info, segment_of_row);
+    return mlr_launched("short_conv");
+}
+
+MLR_API int mlr_short_conv_state(const void* in, int ld_in, int act_bf16, int channels, int taps, float* state,
+                                 long long state_stride, const int* segment_info, int n_segments, cudaStream_t stream) {
+    MLR_REQUIRE(channels > 0 && taps >= 1 && taps <= kMaxTaps, "short_conv_state: %d taps are outside [1, %d]", taps, kMaxTaps);
+    if (n_segments <= 0 || taps == 1) return 0;
+    const dim3 grid(n_segments, (channels + 255) / 256);
+    if (act_bf16)
+        mlr_launch((short_conv_state_kernel<__nv_bfloat16>), dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), ld_in,
+                   channels, taps, state, state_stride, segment_info);
+    else
+        mlr_launch((short_conv_state_kernel<float>), dim3(grid), dim3(256), 0, stream, static_cast<const float*>(in), ld_in, channels,
+                   taps, state, state_stride, segment_info);
+    return mlr_launched("short_conv_state");
+}

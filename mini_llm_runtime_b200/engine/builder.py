@@ -77,6 +77,9 @@ class Buf:
     # wanted rows only, what a product prepared of it or None).  A product that can norm its own input takes
     # it as it is; anyone else asks the runtime to `materialize` it first.
     norm: Optional[tuple] = None
+    # A float32 vector [width] that whoever adds this contribution into the stream must add to every row first
+    # (the bias of a sub-layer's last product, which has no bias operand).
+    bias: Optional[torch.Tensor] = None
 
     @property
     def is_bf16(self) -> int:

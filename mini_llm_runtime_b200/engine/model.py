@@ -109,12 +109,13 @@ class Model:
         self.table_hook = None
         self._hook_sent = None
         self.last_h2d_bytes = 0
-        # A model whose parts all compile (`Part.compiles`) and keep no per-request state runs its steps
-        # in the native executor (programs of launches, CUDA graphs for decode shapes); any other
-        # model is stepped from Python, part by part, without graphs.
+        # A model whose parts all compile (`Part.compiles`) runs its steps in the native executor (programs
+        # of launches, CUDA graphs for decode shapes); any other model is stepped from Python, part by part,
+        # without graphs.  Per-request state of compiled parts lives at fixed addresses (`RunContext.state`,
+        # indexed by the slot of each segment), which programs and graphs name like any weight; a step updates
+        # it in place, once, and a step that fails after its first launch poisons the model anyway.
         self._native: Optional[NativeStepper] = None
-        self._compiles = (all(r.state_need is None for r in self.runs) and all(p.compiles() for p in self._all_parts())
-                          and all(b.compiles() for b in self.blocks))
+        self._compiles = all(p.compiles() for p in self._all_parts()) and all(b.compiles() for b in self.blocks)
         self.use_graphs = True
         # Table width of a graph, in blocks: a graph serves the contexts of one bucket, and its
         # attention launch is planned for the bucket's upper end.  Set to about 1024 tokens when
@@ -161,7 +162,10 @@ class Model:
         for i, run in enumerate(self.runs):
             ctx = run.context
             if run.need is not None and ctx.write_cache:
-                shape = (pages[ctx.group], 2, run.need.kv_heads, config.page_size, run.need.head_dim)
+                if run.need.value_dim is not None:
+                    shape = (pages[ctx.group], run.need.kv_heads * config.page_size * (run.need.head_dim + run.need.value_dim))
+                else:
+                    shape = (pages[ctx.group], 2, run.need.kv_heads, config.page_size, run.need.head_dim)
                 ctx.cache = torch.empty(shape, dtype=self.rt.dtype, device=self.rt.device)
                 if config.fill_nan:
                     ctx.cache.view(torch.uint8).fill_(0xFF)   # all-ones bytes are NaN in both precisions
@@ -209,7 +213,7 @@ class Model:
 
     def cache_bytes_per_token(self) -> int:
         element = 2 if self.rt.is_bf16 else 4
-        return sum(2 * r.need.kv_heads * r.need.head_dim * element for r in self.runs
+        return sum(r.need.kv_heads * (r.need.head_dim + (r.need.value_dim or r.need.head_dim)) * element for r in self.runs
                    if r.need is not None and r.context.write_cache)
 
     def _refuse_if_poisoned(self) -> None:

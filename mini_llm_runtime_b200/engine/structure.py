@@ -35,7 +35,8 @@ class BuiltParts:
         yield from self.positions.values()
         for block in self.blocks:
             yield block.mixer
-            yield block.feed_forward
+            if block.feed_forward is not None:
+                yield block.feed_forward
             yield from block.norms.values()
         yield self.final_norm
         yield self.lm_head
@@ -46,9 +47,11 @@ def build_parts(plan: ModelPlan) -> BuiltParts:
     blocks = []
     for layer in plan.layers:
         mixer = build_part("mixer", layer.mixer)
-        if getattr(mixer, "position_name", None) is not None:
+        if hasattr(mixer, "attach_positions"):
+            mixer.attach_positions(positions)
+        elif getattr(mixer, "position_name", None) is not None:
             mixer.position = positions[mixer.position_name]
-        feed_forward = build_part("feed_forward", layer.feed_forward)
+        feed_forward = build_part("feed_forward", layer.feed_forward) if layer.feed_forward is not None else None
         norms = {slot: build_part("norm", spec) for slot, spec in layer.norms.items()}
         blocks.append(part_class("block", layer.block)(PartSpec(layer.block), mixer, feed_forward, norms))
     return BuiltParts(build_part("embedding", plan.embedding), positions, blocks, build_part("norm", plan.final_norm),

@@ -34,6 +34,7 @@ _SIGNATURES = {
                                    c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                    c_void_p, c_int, c_int, c_void_p, c_void_p],
         "mlr_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "mlr_gated_bias": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32": {
         "mlr_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -81,6 +82,23 @@ _SIGNATURES = {
                                       c_void_p, c_int, c_void_p, c_void_p, c_void_p],
         "mlr_gemv_bf16_prepared": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_longlong, c_int,
                                    c_void_p, c_void_p],
+    },
+    "norm_grouped": {
+        "mlr_group_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                              c_int, c_float, c_int, c_void_p],
+    },
+    "attention_masked": {
+        "mlr_kv_rope_cache": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                              c_int, c_int, c_void_p, c_void_p],
+        "mlr_attention_masked": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    },
+    "recurrence": {
+        "mlr_linear_recurrence": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
+                                  c_int, c_void_p, c_void_p],
+        "mlr_short_conv": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
+                           c_int, c_void_p],
+        "mlr_short_conv_state": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p],
     },
     "weights": {
         "mlr_normal_fill": [c_void_p, c_int, c_longlong, c_ulonglong, c_double, c_int, c_void_p],

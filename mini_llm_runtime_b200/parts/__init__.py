@@ -1,2 +1,2 @@
 """Importing this package registers the built-in parts."""
-from . import attention, block, embedding, mlp, norm, rotary  # noqa: F401
+from . import attention, block, embedding, masked_attention, mlp, norm, parallel, recurrent, rotary  # noqa: F401

@@ -36,10 +36,14 @@ from ..weights.loader import WeightSpec
 @dataclass(frozen=True)
 class CacheNeed:
     """A mixer that keeps keys and values per token: how far back it reads
-    (`window` None = everything) and the page geometry of one layer."""
+    (`window` None = everything) and the page geometry of one layer.  With `value_dim` set the
+    values have a size of their own and a page holds all its keys and then all its values
+    ([kv_head][token][head_dim], then [kv_head][token][value_dim]); the pool is then
+    [pages, kv_heads * page_size * (head_dim + value_dim)]."""
     window: Optional[int]
     kv_heads: int
     head_dim: int
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -161,6 +165,77 @@ class Mixer(Part):
         return _tensor_of(self.emit(b, b.wrap(x), run))
 
 
+class SequenceCore(Mixer):
+    """A mixer of the form  input projections -> core -> output projection, whose core can also run as
+    one of several beside each other (`parts/parallel.py`): the projections of all of them are then one
+    stacked product each, and every core reads its columns of the first and writes its columns of the
+    operand of the second.  A subclass names its input projections in the order its core expects them
+    (`in_roles`: role -> rows), its output projection "o" [width, core_width], builds its constants in
+    `bind_core(tensors, rt, out_scale)` and lists its launches in `emit_core(b, proj, act, run)`: `proj`
+    and `act` are views (a first column and the whole row stride) of the two buffers."""
+    width = 0
+
+    def in_roles(self) -> List[Tuple[str, int]]:
+        raise NotImplementedError
+
+    def core_width(self) -> int:
+        raise NotImplementedError
+
+    def bind_core(self, tensors: Dict[str, torch.Tensor], rt, out_scale: float) -> None:
+        raise NotImplementedError
+
+    def emit_core(self, b, proj, act, run: "RunContext") -> None:
+        raise NotImplementedError
+
+    # ---- what follows from those
+    def in_columns(self) -> Dict[str, int]:
+        columns, at = {}, 0
+        for role, rows in self.in_roles():
+            columns[role] = at
+            at += rows
+        columns[""] = at
+        return columns
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        return ([WeightSpec(w[role], (rows, self.width)) for role, rows in self.in_roles()]
+                + [WeightSpec(w["o"], (self.width, self.core_width()))] + self.extra_weight_specs())
+
+    def extra_weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def stacked_input(self, tensors: Dict[str, torch.Tensor], rt) -> torch.Tensor:
+        return torch.cat([rt.matrix(tensors[self.spec.weights[role]]) for role, _ in self.in_roles()], dim=0)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        self.w_in = pad_rows(self.stacked_input(tensors, rt), 8)
+        self.w_out = rt.matrix(tensors[self.spec.weights["o"]])
+        self.bind_core(tensors, rt, 1.0)
+
+    def emit(self, b, x, run: "RunContext"):
+        rt = b.rt
+        proj = rt.linear(b, x, self.w_in, activation=True)
+        act = b.temp(x.rows, self.core_width(), rt.dtype)
+        self.emit_core(b, proj, act, run)
+        return rt.linear(b, act, self.w_out, out_dtype=torch.float32)
+
+
+def pad_rows(w: torch.Tensor, multiple: int) -> torch.Tensor:
+    """`w` with zero rows added up to a multiple (a stacked product's output rows then start on 16-byte borders)."""
+    extra = -w.shape[0] % multiple
+    if not extra:
+        return w.contiguous()
+    return torch.cat([w, torch.zeros((extra, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0).contiguous()
+
+
+def columns_of(buf, first: int, width: int):
+    """The view [rows, width] of a buffer that starts at column `first` (same rows and row stride)."""
+    from ..engine.builder import Buf
+    size = torch.empty((), dtype=buf.dtype).element_size()
+    tensor = buf.tensor[:, first:first + width] if buf.tensor is not None else None
+    return Buf(buf.ptr + first * size, buf.rows, width, buf.dtype, buf.ld, tensor=tensor)
+
+
 class FeedForward(Part):
     category = "feed_forward"
 
@@ -226,8 +301,8 @@ class Block(Part):
         return None
 
     def compiles(self) -> bool:
-        return (_definer(type(self), "emit") not in _INTERFACES and self.mixer.compiles() and self.feed_forward.compiles()
-                and all(n.compiles() for n in self.norms.values()))
+        return (_definer(type(self), "emit") not in _INTERFACES and self.mixer.compiles()
+                and (self.feed_forward is None or self.feed_forward.compiles()) and all(n.compiles() for n in self.norms.values()))
 
 
 class Embedding(Part):

@@ -39,3 +39,38 @@ class PreNormBlock(Block):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class SandwichBlock(Block):
+    """Norms on both sides of each sub-layer: `h += post(mixer(pre(h)))`, then
+    `h += post(feed_forward(pre(h)))`; a layer without a feed-forward has only the first.
+
+    The sub-layers' results are contributions that a norm stands behind, so they are not added into the
+    stream by their last product; the norm behind a sub-layer adds it and applies the norm before the
+    next sub-layer in the same launch.  Norm slots: "pre_mixer", "post_mixer", "pre_feed_forward",
+    "post_feed_forward"; the norms must offer `emit_residual` (the grouped RMS norm does)."""
+
+    def forward(self, h, pending, step, run):
+        from ..engine.builder import EagerBuilder
+        b = EagerBuilder(step)
+        out = self.emit(b, b.wrap(h), b.wrap(pending), run)
+        return out.tensor if out is not None else None
+
+    def first_norm(self):
+        return self.norms["pre_mixer"]
+
+    def emit(self, b, h, pending, run):
+        b.residual = None            # nothing of this block is added into the stream by a product
+        b.norm_ahead = None
+        x = self.norms["pre_mixer"].emit(b, h, pending)
+        mixed = self.mixer.emit(b, x, run)
+        if self.feed_forward is None:
+            self.norms["post_mixer"].emit_residual(b, h, mixed)
+            return None
+        x = self.norms["post_mixer"].emit_residual(b, h, mixed, then=self.norms["pre_feed_forward"])
+        out = self.feed_forward.emit(b, x)
+        self.norms["post_feed_forward"].emit_residual(b, h, out)
+        return None
+
+
+register_part("block", "sandwich", SandwichBlock)

@@ -1,0 +1,100 @@
+"""Grouped-query attention over the paged cache with the choices that differ between designs as
+parameters: which earlier keys a query sees (all, a window, its own chunk of positions), keys and
+values of different sizes, rotation of only the first values of a head with or without linear
+position scaling, a sink in the softmax, and a gate on the output.
+
+    q, k, v, g = x [Wq; Wk; Wv; Wg]^T             one stacked product
+    k <- rotate(k, position); cache <- k, v       `mlr_kv_rope_cache`
+    o_h = sum_j p_j v_j,  p_j = exp(s_j) / (sink + sum exp(s_j)),  s_j = (rotate(q_h) . k_j) * scale
+          over the keys j <= position that the window and the chunk allow;  sink = 1 (a key of score 0
+          without a value) or 0                    `mlr_attention_masked`
+    o <- o * sigmoid(g)  (or silu, or no gate), times a constant
+    result = o Wo^T                               float32, not added into the stream
+
+Parameters: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, scale, window (None or n), chunk
+(None or n), sink (bool), gate (None | "sigmoid" | "silu"), position (name of a `rotary_frequencies`
+encoding of the plan, or None).  Weights: "q" [H D, W], "k" [G D, W], "v" [G Dv, W], "g" [H Dv, W] (with a
+gate), "o" [W, H Dv].
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.base import ConfigError
+from ..config.registry import register_part
+from ..ops import functions as F
+from ..ops import native
+from ..ops.specs import GATES, MaskedAttentionSpec, address
+from .base import CacheNeed, RunContext, SequenceCore, columns_of
+
+
+class MaskedAttentionMixer(SequenceCore):
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = spec.params
+        self.width = int(p["hidden_size"])
+        self.heads, self.kv_heads = int(p["num_heads"]), int(p["num_kv_heads"])
+        self.dim, self.vdim = int(p["head_dim"]), int(p.get("value_dim") or p["head_dim"])
+        self.scale = float(p["scale"])
+        self.window, self.chunk = p.get("window"), p.get("chunk")
+        self.sink = bool(p.get("sink", False))
+        self.gate = p.get("gate")
+        self.position_name = p.get("position")
+        self.position = None
+        if self.heads % self.kv_heads:
+            raise ConfigError(f"{self.heads} query heads cannot share {self.kv_heads} kv heads")
+        if self.gate not in GATES:
+            raise ConfigError(f"unknown output gate {self.gate!r}")
+        if not (1 <= self.dim <= 1024 and 1 <= self.vdim <= 256):
+            raise ConfigError(f"key size {self.dim} / value size {self.vdim} is outside what the masked attention kernel takes (1024 / 256)")
+        if (self.window is not None and self.window <= 0) or (self.chunk is not None and self.chunk <= 0):
+            raise ConfigError("a window or chunk must be positive")
+        self.desc: Optional[MaskedAttentionSpec] = None
+
+    def attach_positions(self, positions) -> None:
+        if self.position_name is not None:
+            self.position = positions[self.position_name]
+            if self.position.dims > self.dim:
+                raise ConfigError(f"{self.position.dims} rotated values do not fit a head of {self.dim}")
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(self.window, self.kv_heads, self.dim, self.vdim)
+
+    def in_roles(self) -> List[Tuple[str, int]]:
+        roles = [("q", self.heads * self.dim), ("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)]
+        return roles + ([("g", self.heads * self.vdim)] if self.gate else [])
+
+    def core_width(self) -> int:
+        return self.heads * self.vdim
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["attention_masked"] + F.product_modules(dtype)
+
+    def bind_core(self, tensors, rt, out_scale: float) -> None:
+        freq = self.position.frequencies() if self.position is not None else None
+        self._freq = freq
+        self.desc = MaskedAttentionSpec(
+            freq=freq.data_ptr() if freq is not None and freq.numel() else None, heads=self.heads, kv_heads=self.kv_heads, dim=self.dim,
+            vdim=self.vdim, rot_dims=self.position.dims if self.position is not None else 0, window=self.window or 0,
+            chunk=self.chunk or 0, sink=int(self.sink), gate_kind=GATES[self.gate], scale=self.scale, out_scale=float(out_scale))
+
+    def emit_core(self, b, proj, act, run: RunContext) -> None:
+        if run.cache is None or run.cache.dtype is not proj.dtype:
+            raise native.KernelError("masked attention: the cache must have the activations' precision")
+        at = self.in_columns()
+        k = columns_of(proj, at["k"], self.kv_heads * self.dim)
+        v = columns_of(proj, at["v"], self.kv_heads * self.vdim)
+        gate = columns_of(proj, at["g"], self.heads * self.vdim) if self.gate else None
+        table, stride = b.table(run.group), b.table_stride(run.group)
+        if run.write_cache:
+            b.launch("attention_masked", "mlr_kv_rope_cache", address(self.desc), k.ptr, k.ld, v.ptr, v.ld, proj.is_bf16,
+                     run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"), b.meta("segment_of_row"), table, stride,
+                     b.page_size, proj.rows, b.status, b.stream)
+        b.launch("attention_masked", "mlr_attention_masked", address(self.desc), proj.ptr, proj.ld, gate.ptr if gate else None,
+                 gate.ld if gate else 0, act.ptr, act.ld, proj.is_bf16, run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"),
+                 b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, b.status, b.stream)
+
+
+register_part("mixer", "masked_attention", MaskedAttentionMixer)

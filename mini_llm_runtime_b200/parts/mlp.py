@@ -51,3 +51,49 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class GatedBiasFeedForward(FeedForward):
+    """Gated feed-forward whose three projections have biases: `down(act(gate x + b_g) * (up x + b_u)) + b_d`,
+    act = SiLU or the tanh form of GELU.  Gate and up are one stacked product; a row-wise kernel adds their
+    biases and gates; the last bias travels with the result (`Buf.bias`) to whoever adds it into the stream.
+    Parameters: hidden_size, intermediate_size, activation ("silu" | "gelu_tanh").  Weights: "gate", "up"
+    [I, width], "down" [width, I], "gate_bias", "up_bias" [I], "down_bias" [width]."""
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = self.ACTIVATIONS[spec.params.get("activation", "silu")]
+        self.w_gate_up = self.w_down = self.b_gate = self.b_up = self.b_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w = self.spec.weights
+        return [WeightSpec(w["gate"], (self.inter, self.width)), WeightSpec(w["up"], (self.inter, self.width)),
+                WeightSpec(w["down"], (self.width, self.inter)),
+                WeightSpec(w["gate_bias"], (self.inter,), "vector", ("normal", 0.02)),
+                WeightSpec(w["up_bias"], (self.inter,), "vector", ("normal", 0.02)),
+                WeightSpec(w["down_bias"], (self.width,), "vector", ("normal", 0.02))]
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["elementwise"] + F.product_modules(dtype)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        w = self.spec.weights
+        self.w_gate_up = torch.cat([rt.matrix(tensors[w["gate"]]), rt.matrix(tensors[w["up"]])], dim=0).contiguous()
+        self.w_down = rt.matrix(tensors[w["down"]])
+        self.b_gate, self.b_up, self.b_down = (rt.vector(tensors[w[r]]).float() for r in ("gate_bias", "up_bias", "down_bias"))
+
+    def emit(self, b, x):
+        rt = b.rt
+        both = rt.linear(b, x, self.w_gate_up, activation=True)
+        act = b.temp(x.rows, self.inter, rt.dtype)
+        b.launch("elementwise", "mlr_gated_bias", both.ptr, both.ld, self.b_gate.data_ptr(), self.b_up.data_ptr(), act.ptr, act.ld,
+                 act.is_bf16, x.rows, self.inter, self.activation, b.stream)
+        out = rt.linear(b, act, self.w_down, out_dtype=torch.float32)
+        out.bias = self.b_down
+        return out
+
+
+register_part("feed_forward", "gated_bias", GatedBiasFeedForward)

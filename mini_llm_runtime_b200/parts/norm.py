@@ -40,6 +40,8 @@ class RmsNorm(Norm):
         """out[r] = rmsnorm(h[row] + delta[row]) * weight, row = the r-th wanted row or r; unless only
         the wanted rows are normed, the sum is stored back to h, which moves the residual stream on.
         `delta` may be partial sums [S, M, width], which are added in order first."""
+        if delta is not None and getattr(delta, "bias", None) is not None:
+            raise native.KernelError("this norm cannot add the bias its contribution carries")
         count = b.want if wanted_only else h.rows
         prepared, b.prepared = b.prepared, None
         if delta is None and b.rt.norm_can_wait(b, count, self.width):
@@ -59,3 +61,63 @@ class RmsNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RmsNorm)
+
+
+class GroupRmsNorm(Norm):
+    """RMS norm in groups: the vector in `groups` equal consecutive parts, each over its own root mean
+    square, the whole times a weight.  groups = 1 is `rmsnorm` computed by the same kernel.
+
+    Besides the interface of every norm (`emit`: add a pending contribution as it is, then norm) it can
+    stand BEHIND a sub-layer: `emit_residual` adds norm(contribution [+ bias]) * weight into the stream,
+    and in the same launch applies the norm that reads the stream next (`then`), if one is named.
+    Parameters: width, groups, eps.  Weights: "weight" [width]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.width = int(spec.params["width"])
+        self.groups = int(spec.params.get("groups", 1))
+        self.eps = float(spec.params["eps"])
+        if self.groups < 1 or self.width % self.groups:
+            raise ValueError(f"a norm over {self.width} values cannot have {self.groups} equal groups")
+        self.weight: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.spec.weights["weight"], (self.width,), "vector", ("one_plus_normal", 0.01))]
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["norm_grouped"]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
+        self.weight = rt.vector(tensors[self.spec.weights["weight"]]).float()
+
+    def emit(self, b, h, delta, wanted_only: bool = False):
+        if delta is not None and (delta.slices or wanted_only):
+            raise native.KernelError("the grouped norm adds a plain [rows, width] contribution for all rows only")
+        count = b.want if wanted_only else h.rows
+        out = b.temp(count, self.width, b.rt.dtype)
+        bias = getattr(delta, "bias", None) if delta is not None else None
+        b.launch("norm_grouped", "mlr_group_rmsnorm", h.ptr, delta.ptr if delta is not None else None,
+                 delta.ld if delta is not None else 0, bias.data_ptr() if bias is not None else None, None,
+                 self.weight.data_ptr(), out.ptr, out.ld, out.is_bf16, b.meta("want_rows") if wanted_only else None, count,
+                 self.width, self.groups, self.eps, 0, b.stream, need="want" if wanted_only else None)
+        return out
+
+    def emit_residual(self, b, h, delta, then: Optional["GroupRmsNorm"] = None):
+        """h += norm(delta + its bias) * weight; returns then(h) in the activation dtype, or None."""
+        if delta.slices:
+            raise native.KernelError("the grouped norm takes a plain [rows, width] contribution")
+        if then is not None and (then.width, then.groups, then.eps) != (self.width, self.groups, self.eps):
+            out = None
+        else:
+            out = b.temp(h.rows, self.width, b.rt.dtype) if then is not None else None
+        bias = getattr(delta, "bias", None)
+        b.launch("norm_grouped", "mlr_group_rmsnorm", h.ptr, delta.ptr, delta.ld, bias.data_ptr() if bias is not None else None,
+                 self.weight.data_ptr(), then.weight.data_ptr() if out is not None else None,
+                 out.ptr if out is not None else None, out.ld if out is not None else 0, int(b.rt.is_bf16), None, h.rows,
+                 self.width, self.groups, self.eps, 1, b.stream)
+        if then is not None and out is None:
+            return then.emit(b, h, None)
+        return out
+
+
+register_part("norm", "group_rmsnorm", GroupRmsNorm)

@@ -48,3 +48,31 @@ class Rope(PositionEncoding):
 
 
 register_part("position", "rope", Rope)
+
+
+class RotaryFrequencies(PositionEncoding):
+    """Rotation given as its frequencies only: `freq_i = base^(-2i/dims) / factor`, i < dims/2.  The kernels
+    that use it compute `position * freq_i` and its cosine and sine in float32 themselves, so no table
+    exists and no largest position: `factor` > 1 is linear position scaling.  Only the first `dims`
+    values of a head are rotated (value i with value i + dims/2); a mixer's heads may be wider.
+    Parameters: base, dims, factor (default 1).  No weights."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.base = float(spec.params["base"])
+        self.dims = int(spec.params["dims"])
+        self.factor = float(spec.params.get("factor", 1.0))
+        if self.dims < 0 or self.dims % 2 or self.base <= 0 or self.factor <= 0:
+            raise ValueError(f"a rotation of {self.dims} values with base {self.base} and factor {self.factor} is not defined")
+        self._freq: Optional[torch.Tensor] = None
+
+    def bind(self, tensors, rt) -> None:
+        i = np.arange(self.dims // 2, dtype=np.float64)
+        freq = np.power(self.base, -2.0 * i / max(self.dims, 1)) / self.factor
+        self._freq = torch.from_numpy(freq.astype(np.float32)).to(rt.device)
+
+    def frequencies(self) -> torch.Tensor:
+        return self._freq
+
+
+register_part("position", "rotary_frequencies", RotaryFrequencies)
