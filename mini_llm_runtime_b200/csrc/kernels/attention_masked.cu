@@ -15,7 +15,9 @@
 // values; `mlr_attention_masked` rotates its query as it loads it and walks the visible keys in tiles
 // of 64 with a running maximum, one block per (row, query head), so a row's result depends on its
 // position and on the cache only.  Scores, weights and sums are float32; q, the cache, the gate and
-// the output are float32 or bfloat16.  Keys that are not visible are never loaded.
+// the output are float32 or bfloat16.  Keys that are not visible are never loaded.  That kernel serves
+// decoded tokens, short portions and the float32 path; `mlr_attention_masked_tiles` (below) takes the
+// prompt portions of the bfloat16 path in tiles of 64 rows on the tensor cores.
 #include "common.cuh"
 
 struct MaskedAttentionSpec {
@@ -31,6 +33,7 @@ namespace {
 constexpr int kTile = 64;
 constexpr int kThreads = 128;
 constexpr int kMaxDimsPerThread = 2;  // vdim <= 256
+constexpr int kRowsPerItem = 16;      // a segment that the planner gives the row kernel brings at most this many rows
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int ld_k, const T* v, int ld_v, T* cache, int num_pages,
@@ -76,7 +79,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
                                                                     const T* cache, int num_pages, const int* positions,
                                                                     const int* segment_of_row, const int* block_table,
                                                                     int table_stride, int page_size, MaskedAttentionSpec s,
-                                                                    int* status) {
+                                                                    const int* items, const int* segment_info, int* status) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -85,7 +88,14 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     float* qs = scores + kTile;                                  // [dim]
     __shared__ int bad;
 
-    const int row = blockIdx.x, head = blockIdx.y;
+    int row = blockIdx.x;
+    if (segment_info) {         // blockIdx.x = (segment of few rows, row of it); `items` lists those segments, or all are
+        const int item = blockIdx.x / kRowsPerItem, j = blockIdx.x % kRowsPerItem;
+        const int* info = segment_info + 4 * (items ? items[item] : item);
+        if (j >= info[1]) return;
+        row = info[0] + j;
+    }
+    const int head = blockIdx.y;
     const int kv_head = head / (s.heads / s.kv_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int position = positions[row];
@@ -189,6 +199,211 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     }
 }
 
+// ---- prompt portions in bfloat16: 64 query rows of one request and one head per block, on the tensor cores.
+// S = Q K^T by mma.sync (bfloat16 operands, float32 sums: the scores are exact products summed in float32); mask, sink
+// and the running softmax in float32; the weights enter P V as TWO bfloat16 terms (p = hi + lo, 16 bits of
+// mantissa) against the bfloat16 values, again with float32 sums.  Keys and values of a tile of 64 positions are
+// copied from their pages into shared memory (zeros where no row of the block may look).
+constexpr int kRows = 64, kKeys = 64, kPad = 8;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ int first_visible(int position, const MaskedAttentionSpec& s) {
+    int lo = 0;
+    if (s.window > 0) lo = max(lo, position - s.window + 1);
+    if (s.chunk > 0) lo = max(lo, (position / s.chunk) * s.chunk);
+    return lo;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_bfloat16* q, int ldq, const __nv_bfloat16* gate, int ld_gate,
+                                                                    __nv_bfloat16* out, int ldo, const __nv_bfloat16* cache, int num_pages,
+                                                                    const int* tiles, const int* segment_info, const int* block_table,
+                                                                    int table_stride, int page_size, MaskedAttentionSpec s, int* status) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int qstride = s.dim + kPad, vstride = s.vdim + kPad;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);
+    __nv_bfloat16* Ks = Qs + kRows * qstride;
+    __nv_bfloat16* Vs = Ks + kKeys * qstride;
+    __shared__ int bad;
+
+    const int head = blockIdx.x, kv_head = head / (s.heads / s.kv_heads);
+    const int segment = tiles[2 * blockIdx.y], tile_token = tiles[2 * blockIdx.y + 1];
+    const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], start = segment_info[4 * segment + 2];
+    const int n_rows = min(kRows, count - tile_token);
+    const int first_pos = start + tile_token, last_pos = first_pos + n_rows - 1;
+    const int lo_min = first_visible(first_pos, s);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int* table = block_table + static_cast<size_t>(segment) * table_stride;
+    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.dim + s.vdim);
+    const size_t key_plane = static_cast<size_t>(s.kv_heads) * page_size * s.dim;
+    if (threadIdx.x == 0) bad = 0;
+
+    // The block's queries, rotated in float32, as bfloat16.
+    const int half = s.rot_dims / 2;
+    for (int i = threadIdx.x; i < kRows * s.dim; i += 128) {
+        const int r = i / s.dim, c = i % s.dim;
+        float value = 0.0f;
+        if (r < n_rows) {
+            const __nv_bfloat16* qrow = q + static_cast<size_t>(first + tile_token + r) * ldq + static_cast<size_t>(head) * s.dim;
+            value = __bfloat162float(qrow[c]);
+            if (c < s.rot_dims) {
+                float sn, cs;
+                sincosf(static_cast<float>(first_pos + r) * s.freq[c < half ? c : c - half], &sn, &cs);
+                const float other = __bfloat162float(qrow[c < half ? c + half : c - half]);
+                value = c < half ? value * cs - other * sn : value * cs + other * sn;
+            }
+        }
+        Qs[r * qstride + c] = __float2bfloat16_rn(value);
+    }
+
+    const int r0 = warp * 16;
+    const int pos_a = first_pos + r0 + g, pos_b = pos_a + 8;         // this thread's two rows
+    const bool row_a = r0 + g < n_rows, row_b = r0 + g + 8 < n_rows;
+    const int lo_a = first_visible(pos_a, s), lo_b = first_visible(pos_b, s);
+    float m_a = s.sink ? 0.0f : -INFINITY, m_b = m_a, l_a = s.sink ? 1.0f : 0.0f, l_b = l_a;   // l: this thread's share, but the sink's 1
+    if (t != 0) l_a = l_b = 0.0f;                                                                // is counted once per row
+    float O[NV][4];
+#pragma unroll
+    for (int nv = 0; nv < NV; ++nv) O[nv][0] = O[nv][1] = O[nv][2] = O[nv][3] = 0.0f;
+    const int ksteps = s.dim / 16;
+    const uint32_t vs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs));
+
+    for (int kt = (lo_min / kKeys) * kKeys; kt <= last_pos; kt += kKeys) {
+        __syncthreads();      // the tile before is no longer read (and Qs is written)
+        const int kchunks = s.dim / 8, vchunks = s.vdim / 8;
+        for (int i = threadIdx.x; i < kKeys * (kchunks + vchunks); i += 128) {
+            const int key = i / (kchunks + vchunks), c = i % (kchunks + vchunks);
+            const int position = kt + key;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (position >= lo_min && position <= last_pos) {
+                const int page = table[position / page_size];
+                if (page < 0 || page >= num_pages) {
+                    bad = 1;
+                } else {
+                    const size_t in_page = static_cast<size_t>(kv_head) * page_size + position % page_size;
+                    const __nv_bfloat16* src = c < kchunks ? cache + page * page_elems + in_page * s.dim + c * 8
+                                                           : cache + page * page_elems + key_plane + in_page * s.vdim + (c - kchunks) * 8;
+                    value = *reinterpret_cast<const uint4*>(src);
+                }
+            }
+            __nv_bfloat16* dst = c < kchunks ? Ks + key * qstride + c * 8 : Vs + key * vstride + (c - kchunks) * 8;
+            *reinterpret_cast<uint4*>(dst) = value;
+        }
+        __syncthreads();
+        float S[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.0f;
+        for (int ks = 0; ks < ksteps; ++ks) {
+            uint32_t a[4];
+            const __nv_bfloat16* qa = Qs + (r0 + g) * qstride + ks * 16 + 2 * t;
+            a[0] = *reinterpret_cast<const uint32_t*>(qa);
+            a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * qstride);
+            a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * qstride + 8);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const __nv_bfloat16* kb = Ks + (nt * 8 + g) * qstride + ks * 16 + 2 * t;
+                mma_bf16(S[nt], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+            }
+        }
+        // mask, running maximum
+        float tile_a = -INFINITY, tile_b = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = kt + nt * 8 + 2 * t + (e & 1);
+                const bool upper = e < 2;
+                const bool seen = upper ? (row_a && key <= pos_a && key >= lo_a) : (row_b && key <= pos_b && key >= lo_b);
+                const float v = seen ? S[nt][e] * s.scale : -INFINITY;
+                S[nt][e] = v;
+                if (upper) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
+            }
+        tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 1));
+        tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 2));
+        tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 1));
+        tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 2));
+        const float new_a = fmaxf(m_a, tile_a), new_b = fmaxf(m_b, tile_b);
+        const float alpha_a = (m_a == -INFINITY) ? 0.0f : expf(m_a - new_a);
+        const float alpha_b = (m_b == -INFINITY) ? 0.0f : expf(m_b - new_b);
+        m_a = new_a;
+        m_b = new_b;
+        l_a *= alpha_a;
+        l_b *= alpha_b;
+#pragma unroll
+        for (int nv = 0; nv < NV; ++nv) {
+            O[nv][0] *= alpha_a; O[nv][1] *= alpha_a; O[nv][2] *= alpha_b; O[nv][3] *= alpha_b;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float m = e < 2 ? new_a : new_b;
+                const float p = S[nt][e] == -INFINITY ? 0.0f : expf(S[nt][e] - m);
+                S[nt][e] = p;
+                if (e < 2) l_a += p; else l_b += p;
+            }
+        // O += P V, P as hi + lo
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float p0 = S[2 * kk + (j >> 1)][(j & 1) * 2], p1 = S[2 * kk + (j >> 1)][(j & 1) * 2 + 1];
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
+                hi[j] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
+                lo[j] = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+            }
+            const uint32_t row_addr = vs_base + static_cast<uint32_t>(((kk * 16 + (lane & 15)) * vstride) * 2);
+#pragma unroll
+            for (int nv = 0; nv < NV; ++nv) {
+                if (nv * 8 < s.vdim) {
+                    uint32_t b0, b1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(row_addr + nv * 16));
+                    mma_bf16(O[nv], hi, b0, b1);
+                    mma_bf16(O[nv], lo, b0, b1);
+                }
+            }
+        }
+    }
+    if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+#pragma unroll
+    for (int nv = 0; nv < NV; ++nv) {
+        if (nv * 8 >= s.vdim) continue;
+        const int col = head * s.vdim + nv * 8 + 2 * t;
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            if (!(hb ? row_b : row_a)) continue;
+            const float l = hb ? l_b : l_a;
+            float v0 = l > 0.0f ? O[nv][2 * hb] / l : 0.0f, v1 = l > 0.0f ? O[nv][2 * hb + 1] / l : 0.0f;
+            const size_t row = static_cast<size_t>(first + tile_token + r0 + g + 8 * hb);
+            if (gate) {
+                const float g0 = __bfloat162float(gate[row * ld_gate + col]), g1 = __bfloat162float(gate[row * ld_gate + col + 1]);
+                const float s0 = 1.0f / (1.0f + expf(-g0)), s1 = 1.0f / (1.0f + expf(-g1));
+                v0 *= s.gate_kind == 2 ? g0 * s0 : s0;
+                v1 *= s.gate_kind == 2 ? g1 * s1 : s1;
+            }
+            *reinterpret_cast<__nv_bfloat162*>(out + row * ldo + col) = __floats2bfloat162_rn(v0 * s.out_scale, v1 * s.out_scale);
+        }
+    }
+}
+
 int check_spec(const MaskedAttentionSpec* s, const char* who) {
     MLR_REQUIRE(s, "%s: no description", who);
     MLR_REQUIRE(s->heads > 0 && s->kv_heads > 0 && s->heads % s->kv_heads == 0, "%s: %d query heads cannot share %d kv heads", who,
@@ -225,8 +440,11 @@ MLR_API int mlr_kv_rope_cache(const MaskedAttentionSpec* spec, const void* k, in
 MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q, int ldq, const void* gate, int ld_gate, void* out,
                                  int ldo, int act_bf16, const void* cache, int num_pages, const int* positions,
                                  const int* segment_of_row, const int* block_table, int table_stride, int page_size, int rows,
-                                 int* status, cudaStream_t stream) {
+                                 const int* items, int n_items, const int* segment_info, int* status, cudaStream_t stream) {
+    // With `segment_info` the kernel runs over `n_items` segments of at most 16 rows each (`items` lists them; null: the
+    // step's first n_items segments) and `rows` is not used; without it, over all `rows` rows.
     if (check_spec(spec, "attention_masked")) return 1;
+    if (segment_info) rows = n_items * kRowsPerItem;
     MLR_REQUIRE(rows >= 0 && page_size > 0 && num_pages > 0, "attention_masked: bad page size or page count");
     MLR_REQUIRE(ldq >= spec->heads * spec->dim && ldo >= spec->heads * spec->vdim, "attention_masked: a row stride is smaller than the row");
     MLR_REQUIRE((spec->gate_kind == 0) == (gate == nullptr), "attention_masked: the description and the call disagree about a gate");
@@ -237,10 +455,47 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
         mlr_launch((attention_masked_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream,
                    static_cast<const __nv_bfloat16*>(q), ldq, static_cast<const __nv_bfloat16*>(gate), ld_gate,
                    static_cast<__nv_bfloat16*>(out), ldo, static_cast<const __nv_bfloat16*>(cache), num_pages, positions, segment_of_row,
-                   block_table, table_stride, page_size, *spec, status);
+                   block_table, table_stride, page_size, *spec, items, segment_info, status);
     else
         mlr_launch((attention_masked_kernel<float>), dim3(grid), dim3(kThreads), shared, stream, static_cast<const float*>(q), ldq,
                    static_cast<const float*>(gate), ld_gate, static_cast<float*>(out), ldo, static_cast<const float*>(cache), num_pages,
-                   positions, segment_of_row, block_table, table_stride, page_size, *spec, status);
+                   positions, segment_of_row, block_table, table_stride, page_size, *spec, items, segment_info, status);
     return mlr_launched("attention_masked");
+}
+
+// Whether the tiled kernel takes these sizes (bfloat16 only): 1 yes, 0 no.
+MLR_API int mlr_attention_masked_tiles_fit(int dim, int vdim) {
+    return dim % 16 == 0 && dim >= 16 && dim <= 256 && vdim % 8 == 0 && vdim >= 8 && vdim <= 128;
+}
+
+// tiles: n_tiles pairs {segment, first token of a tile of up to 64 rows of that segment}.
+MLR_API int mlr_attention_masked_tiles(const MaskedAttentionSpec* spec, const void* q, int ldq, const void* gate, int ld_gate, void* out,
+                                       int ldo, const void* cache, int num_pages, const int* tiles, int n_tiles,
+                                       const int* segment_info, const int* block_table, int table_stride, int page_size, int* status,
+                                       cudaStream_t stream) {
+    if (check_spec(spec, "attention_masked_tiles")) return 1;
+    MLR_REQUIRE(mlr_attention_masked_tiles_fit(spec->dim, spec->vdim), "attention_masked_tiles: key size %d / value size %d not taken",
+                spec->dim, spec->vdim);
+    MLR_REQUIRE(n_tiles >= 0 && n_tiles <= 65535 && page_size > 0 && num_pages > 0, "attention_masked_tiles: bad tile count or pages");
+    MLR_REQUIRE(ldq >= spec->heads * spec->dim && ldo >= spec->heads * spec->vdim && ldo % 2 == 0 && (spec->heads * spec->vdim) % 2 == 0,
+                "attention_masked_tiles: bad row strides");
+    MLR_REQUIRE((spec->gate_kind == 0) == (gate == nullptr), "attention_masked_tiles: the description and the call disagree about a gate");
+    MLR_REQUIRE(reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0, "attention_masked_tiles: alignment");
+    if (n_tiles == 0) return 0;
+    const size_t shared = sizeof(__nv_bfloat16) * (static_cast<size_t>(kRows + kKeys) * (spec->dim + kPad) + kKeys * (spec->vdim + kPad));
+    const dim3 grid(spec->heads, n_tiles);
+#define MLR_TILES(NV)                                                                                                              \
+    do {                                                                                                                           \
+        cudaFuncSetAttribute(attention_masked_tile_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)); \
+        mlr_launch((attention_masked_tile_kernel<NV>), dim3(grid), dim3(128), shared, stream, static_cast<const __nv_bfloat16*>(q), ldq, \
+                   static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(out), ldo,                         \
+                   static_cast<const __nv_bfloat16*>(cache), num_pages, tiles, segment_info, block_table, table_stride, page_size, \
+                   *spec, status);                                                                                                 \
+    } while (0)
+    if (spec->vdim <= 32) MLR_TILES(4);
+    else if (spec->vdim <= 64) MLR_TILES(8);
+    else if (spec->vdim <= 96) MLR_TILES(12);
+    else MLR_TILES(16);
+#undef MLR_TILES
+    return mlr_launched("attention_masked_tiles");
 }

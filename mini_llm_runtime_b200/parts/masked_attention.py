@@ -92,9 +92,24 @@ class MaskedAttentionMixer(SequenceCore):
             b.launch("attention_masked", "mlr_kv_rope_cache", address(self.desc), k.ptr, k.ld, v.ptr, v.ld, proj.is_bf16,
                      run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"), b.meta("segment_of_row"), table, stride,
                      b.page_size, proj.rows, b.status, b.stream)
-        b.launch("attention_masked", "mlr_attention_masked", address(self.desc), proj.ptr, proj.ld, gate.ptr if gate else None,
-                 gate.ld if gate else 0, act.ptr, act.ld, proj.is_bf16, run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"),
-                 b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, b.status, b.stream)
+        args = (address(self.desc), proj.ptr, proj.ld, gate.ptr if gate else None, gate.ld if gate else 0, act.ptr, act.ld)
+        where = (run.cache.data_ptr(), run.cache.shape[0])
+        tiled = (proj.dtype is torch.bfloat16 and native.module("attention_masked").mlr_attention_masked_tiles_fit(self.dim, self.vdim)
+                 and act.ld % 2 == 0)
+        if not tiled:
+            # One block per (row, head): the float32 path, and sizes the tiled kernel does not take.
+            b.launch("attention_masked", "mlr_attention_masked", *args, proj.is_bf16, *where, b.meta("positions"),
+                     b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, b.status, b.stream)
+            return
+        # The step's launch plan (made by the native executor from the step's segments, shared by all layers):
+        # segments of few rows (a decoded token, a short portion) go to the row kernel, prompt portions in tiles of 64
+        # rows to the tensor-core kernel.
+        plan = b.plan((self.heads // self.kv_heads if self.heads // self.kv_heads <= 16 else 1, self.kv_heads, 0, 0, self.dim, 1))
+        info = b.meta("segment_info")
+        b.launch("attention_masked", "mlr_attention_masked", *args, 1, *where, b.meta("positions"), b.meta("segment_of_row"), table,
+                 stride, b.page_size, 0, plan.items, plan.n_items, info, b.status, b.stream, need=plan.n_items)
+        b.launch("attention_masked", "mlr_attention_masked_tiles", *args, *where, plan.tiles, plan.n_tiles, info, table, stride,
+                 b.page_size, b.status, b.stream, need=plan.n_tiles)
 
 
 register_part("mixer", "masked_attention", MaskedAttentionMixer)

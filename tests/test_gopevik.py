@@ -161,7 +161,7 @@ def test_gated_bias_kernel(activation):
     assert torch.allclose(out.cpu().double(), act * up, atol=1e-5, rtol=1e-5)
 
 
-def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, window, sink, gate, T, page, boost=None, seed=0):
+def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, window, sink, gate, T, page, boost=None, seed=0, tiled=0):
     """One request of T tokens written into a paged cache with shuffled pages, then every row's attention."""
     from mini_llm_runtime_b200.ops import native
     from mini_llm_runtime_b200.ops.specs import GATES, MaskedAttentionSpec
@@ -193,11 +193,19 @@ def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, 
     _call("attention_masked", "mlr_kv_rope_cache", ctypes.addressof(spec), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), is16,
           cache.data_ptr(), n_pages, positions.data_ptr(), of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T,
           status.data_ptr(), native.stream())
-    out = torch.empty(T, heads * vdim, dtype=dtype, device=dev)
-    _call("attention_masked", "mlr_attention_masked", ctypes.addressof(spec), q.data_ptr(), q.stride(0),
-          gates.data_ptr() if gate else None, gates.stride(0) if gate else 0, out.data_ptr(), out.stride(0), is16, cache.data_ptr(),
-          n_pages, positions.data_ptr(), of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, status.data_ptr(),
-          native.stream())
+    out = torch.full((T, heads * vdim), float("nan"), dtype=dtype, device=dev)
+    common = (ctypes.addressof(spec), q.data_ptr(), q.stride(0), gates.data_ptr() if gate else None, gates.stride(0) if gate else 0,
+              out.data_ptr(), out.stride(0))
+    if tiled:       # the request's rows in two steps' worth of tiles: a first portion of `tiled` rows, then the rest
+        info = torch.tensor([[0, tiled, 0, 0], [tiled, T - tiled, tiled, 0]], dtype=torch.int32, device=dev)
+        tiles = [(0, t) for t in range(0, tiled, 64)] + [(1, t) for t in range(0, T - tiled, 64)]
+        tiles = torch.tensor(tiles, dtype=torch.int32, device=dev)
+        two = torch.cat([table, table]).contiguous()
+        _call("attention_masked", "mlr_attention_masked_tiles", *common, cache.data_ptr(), n_pages, tiles.data_ptr(), tiles.shape[0],
+              info.data_ptr(), two.data_ptr(), two.stride(0), page, status.data_ptr(), native.stream())
+    else:
+        _call("attention_masked", "mlr_attention_masked", *common, is16, cache.data_ptr(), n_pages, positions.data_ptr(),
+              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, None, 0, None, status.data_ptr(), native.stream())
     assert int(status.item()) == 0
     pos = torch.arange(T)
     qd = plain.rotate_half(q.double().cpu().view(T, heads, dim), pos, rot_dims, base, factor) if rot_dims else q.double().cpu().view(T, heads, dim)
@@ -241,6 +249,31 @@ def test_masked_attention_kernel(dtype, case):
     got, want = _attention_case(dtype, **case)
     tol = 2e-5 if dtype is torch.float32 else 3e-2
     assert torch.allclose(got, want, atol=tol, rtol=tol), float((got - want).abs().max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [
+    dict(heads=4, kv_heads=2, dim=32, vdim=16, rot_dims=8, factor=1.0, chunk=24, window=None, sink=True, gate="sigmoid", T=200, page=16, tiled=70),
+    dict(heads=3, kv_heads=3, dim=16, vdim=40, rot_dims=16, factor=4.0, chunk=100, window=None, sink=True, gate=None, T=333, page=4, tiled=1),
+    dict(heads=2, kv_heads=1, dim=96, vdim=96, rot_dims=0, factor=1.0, chunk=None, window=None, sink=False, gate="silu", T=150, page=16, tiled=64),
+    dict(heads=2, kv_heads=2, dim=16, vdim=8, rot_dims=16, factor=1.0, chunk=None, window=33, sink=False, gate=None, T=190, page=8, tiled=129),
+    dict(heads=1, kv_heads=1, dim=128, vdim=128, rot_dims=64, factor=2.0, chunk=64, window=None, sink=True, gate="sigmoid", T=260, page=16, tiled=100),
+    dict(heads=1, kv_heads=1, dim=256, vdim=104, rot_dims=2, factor=1.0, chunk=130, window=None, sink=True, gate=None, T=270, page=16, tiled=5),
+])
+def test_masked_attention_in_tiles_on_the_tensor_cores(case):
+    """Prompt portions in bfloat16: tiles of 64 rows of two portions of one request, the second continuing the first."""
+    got, want = _attention_case(torch.bfloat16, **case)
+    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), float((got - want).abs().max())
+
+
+@pytest.mark.gpu
+def test_a_loud_key_at_the_chunk_border_in_tiles():
+    for chunk, T in ((64, 200), (50, 230)):
+        start = (T - 1) // chunk * chunk
+        for key in (start, start - 1):
+            got, want = _attention_case(torch.bfloat16, heads=2, kv_heads=1, dim=16, vdim=8, rot_dims=4, factor=1.0, chunk=chunk, window=None,
+                                        sink=True, gate=None, T=T, page=16, boost=key, seed=key, tiled=T - 3)
+            assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (chunk, key, float((got - want).abs().max()))
 
 
 @pytest.mark.gpu
