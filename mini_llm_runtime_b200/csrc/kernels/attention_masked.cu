@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
 // S = Q K^T by mma.sync (bfloat16 operands, float32 sums: the scores are exact products summed in float32); mask, sink
 // and the running softmax in float32; the weights enter P V as TWO bfloat16 terms (p = hi + lo, 16 bits of
 // mantissa) against the bfloat16 values, again with float32 sums.  Keys and values of a tile of 64 positions are
-// copied from their pages into shared memory (zeros where no row of the block may look).
+// copied from their pages into shared memory (zeros where no row of the block may look), one tile ahead.
 constexpr int kRows = 64, kKeys = 64, kPad = 8;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int qstride = s.dim + kPad, vstride = s.vdim + kPad;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem);
     __nv_bfloat16* Ks = Qs + kRows * qstride;
-    __nv_bfloat16* Vs = Ks + kKeys * qstride;
+    __nv_bfloat16* Vs = Ks + 2 * kKeys * qstride;        // two stages of each
     __shared__ int bad;
 
     const int head = blockIdx.x, kv_head = head / (s.heads / s.kv_heads);
@@ -280,28 +280,41 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int ksteps = s.dim / 16;
     const uint32_t vs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs));
 
-    for (int kt = (lo_min / kKeys) * kKeys; kt <= last_pos; kt += kKeys) {
-        __syncthreads();      // the tile before is no longer read (and Qs is written)
-        const int kchunks = s.dim / 8, vchunks = s.vdim / 8;
+    // Keys and values of a tile of 64 positions go from their pages into one of two stages by asynchronous copies, so
+    // that the next tile arrives while this one is multiplied; rows no query of the block may see become zeros.
+    const int kchunks = s.dim / 8, vchunks = s.vdim / 8;
+    auto fetch = [&](int kt, int into) {
+        __nv_bfloat16* kdst = Ks + into * kKeys * qstride;
+        __nv_bfloat16* vdst = Vs + into * kKeys * vstride;
         for (int i = threadIdx.x; i < kKeys * (kchunks + vchunks); i += 128) {
             const int key = i / (kchunks + vchunks), c = i % (kchunks + vchunks);
             const int position = kt + key;
-            uint4 value = make_uint4(0, 0, 0, 0);
-            if (position >= lo_min && position <= last_pos) {
+            const __nv_bfloat16* src = cache;
+            bool real = position >= lo_min && position <= last_pos;
+            if (real) {
                 const int page = table[position / page_size];
                 if (page < 0 || page >= num_pages) {
                     bad = 1;
+                    real = false;
                 } else {
                     const size_t in_page = static_cast<size_t>(kv_head) * page_size + position % page_size;
-                    const __nv_bfloat16* src = c < kchunks ? cache + page * page_elems + in_page * s.dim + c * 8
-                                                           : cache + page * page_elems + key_plane + in_page * s.vdim + (c - kchunks) * 8;
-                    value = *reinterpret_cast<const uint4*>(src);
+                    src = c < kchunks ? cache + page * page_elems + in_page * s.dim + c * 8
+                                      : cache + page * page_elems + key_plane + in_page * s.vdim + (c - kchunks) * 8;
                 }
             }
-            __nv_bfloat16* dst = c < kchunks ? Ks + key * qstride + c * 8 : Vs + key * vstride + (c - kchunks) * 8;
-            *reinterpret_cast<uint4*>(dst) = value;
+            mlr_async_copy16(c < kchunks ? kdst + key * qstride + c * 8 : vdst + key * vstride + (c - kchunks) * 8, src, real);
         }
-        __syncthreads();
+        mlr_async_commit();
+    };
+    const int kt_first = (lo_min / kKeys) * kKeys;
+    fetch(kt_first, 0);
+    int current = 0;
+    for (int kt = kt_first; kt <= last_pos; kt += kKeys, current ^= 1) {
+        mlr_async_wait();
+        __syncthreads();      // this tile has arrived (and Qs is written); no warp still reads the other stage
+        if (kt + kKeys <= last_pos) fetch(kt + kKeys, current ^ 1);
+        const __nv_bfloat16* Kt = Ks + current * kKeys * qstride;
+        const uint32_t vt_base = vs_base + static_cast<uint32_t>(current * kKeys * vstride * 2);
         float S[8][4];
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.0f;
@@ -314,7 +327,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
             a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * qstride + 8);
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                const __nv_bfloat16* kb = Ks + (nt * 8 + g) * qstride + ks * 16 + 2 * t;
+                const __nv_bfloat16* kb = Kt + (nt * 8 + g) * qstride + ks * 16 + 2 * t;
                 mma_bf16(S[nt], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
             }
         }
@@ -366,7 +379,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                 hi[j] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
                 lo[j] = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
             }
-            const uint32_t row_addr = vs_base + static_cast<uint32_t>(((kk * 16 + (lane & 15)) * vstride) * 2);
+            const uint32_t row_addr = vt_base + static_cast<uint32_t>(((kk * 16 + (lane & 15)) * vstride) * 2);
 #pragma unroll
             for (int nv = 0; nv < NV; ++nv) {
                 if (nv * 8 < s.vdim) {
@@ -482,7 +495,7 @@ MLR_API int mlr_attention_masked_tiles(const MaskedAttentionSpec* spec, const vo
     MLR_REQUIRE((spec->gate_kind == 0) == (gate == nullptr), "attention_masked_tiles: the description and the call disagree about a gate");
     MLR_REQUIRE(reinterpret_cast<uintptr_t>(cache) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0, "attention_masked_tiles: alignment");
     if (n_tiles == 0) return 0;
-    const size_t shared = sizeof(__nv_bfloat16) * (static_cast<size_t>(kRows + kKeys) * (spec->dim + kPad) + kKeys * (spec->vdim + kPad));
+    const size_t shared = sizeof(__nv_bfloat16) * (static_cast<size_t>(kRows + 2 * kKeys) * (spec->dim + kPad) + 2 * kKeys * (spec->vdim + kPad));
     const dim3 grid(spec->heads, n_tiles);
 #define MLR_TILES(NV)                                                                                                              \
     do {                                                                                                                           \

@@ -211,6 +211,19 @@ __device__ __forceinline__ void mlr_store8(__nv_bfloat16* p, const float (&v)[8]
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---- asynchronous copies global -> shared (fire and forget; a thread waits for its own with mlr_async_wait) ----
+__device__ __forceinline__ void mlr_async_copy16(void* shared_dst, const void* global_src, bool real = true) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(shared_dst));
+    const int bytes = real ? 16 : 0;       // 0: nothing is read and the 16 bytes become zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(global_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mlr_async_copy4(void* shared_dst, const void* global_src) {
+    const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(shared_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(global_src) : "memory");
+}
+__device__ __forceinline__ void mlr_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void mlr_async_wait() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
 __device__ __forceinline__ float mlr_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

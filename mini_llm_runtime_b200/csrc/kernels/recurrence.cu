@@ -229,6 +229,256 @@ __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, 
         }
 }
 
+// ---- the same in three kernels, for steps of many rows.  The fused kernel above has one block per (request, head):
+// a long prompt of one request then runs on a handful of SMs, and every block prepares q and k itself.  Here the
+// preparation and the read-out are parallel over rows, and the scan, the only sequential part, has a block per
+// (request, head, group of 16 columns of the state).
+
+// q and k of every row, prepared, as float32 [rows, qk_heads * dim] each; for the delta rule also g and beta [rows, 2 * heads].
+template <typename T>
+__global__ void __launch_bounds__(128) recurrence_prepare_kernel(const T* proj, int ld, const T* side, int ld_side, float* qf, float* kf,
+                                                                 float* gates, const int* positions, RecurrenceSpec s) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const T* in = proj + static_cast<size_t>(row) * ld;
+    const float position = static_cast<float>(positions[row]);
+    const int half = s.rot_dims / 2;
+    const size_t out_ld = static_cast<size_t>(s.qk_heads) * s.dim;
+    for (int vec = warp; vec < 2 * s.qk_heads; vec += warps) {
+        const bool is_q = vec < s.qk_heads;
+        const int head = is_q ? vec : vec - s.qk_heads;
+        const T* x = in + (is_q ? s.col_q : s.col_k) + head * s.dim;
+        float* y = (is_q ? qf : kf) + row * out_ld + static_cast<size_t>(head) * s.dim;
+        const float mult = is_q ? s.q_mult : s.k_mult;
+        if (s.prep == 1) {
+            for (int c = lane; c < half; c += 32) {
+                float sn, cs;
+                sincosf(position * s.freq[c], &sn, &cs);
+                const float u = mlr_load(x, c), v = mlr_load(x, c + half);
+                y[c] = (u * cs - v * sn) * mult;
+                y[c + half] = (v * cs + u * sn) * mult;
+            }
+            for (int c = s.rot_dims + lane; c < s.dim; c += 32) y[c] = mlr_load(x, c) * mult;
+        } else if (s.prep == 2) {
+            float sum = 0.0f;
+            for (int c = lane; c < s.dim; c += 32) {
+                const float v = mlr_load(x, c);
+                sum = fmaf(v, v, sum);
+            }
+            const float inv = 1.0f / sqrtf(mlr_warp_sum(sum) + s.unit_eps);
+            for (int c = lane; c < s.dim; c += 32) y[c] = mlr_load(x, c) * inv * mult;
+        } else {
+            for (int c = lane; c < s.dim; c += 32) y[c] = mlr_load(x, c) * mult;
+        }
+    }
+    if (s.rule == 1) {
+        const T* sd = side + static_cast<size_t>(row) * ld_side;
+        for (int h = threadIdx.x; h < s.heads; h += blockDim.x) {
+            const float a = mlr_load(sd, s.col_a + h), b = mlr_load(sd, s.col_b + h);
+            gates[static_cast<size_t>(row) * 2 * s.heads + h] = expf(-expf(s.a_log[h]) * softplus(a + s.dt_bias[h]));
+            gates[static_cast<size_t>(row) * 2 * s.heads + s.heads + h] = 1.0f / (1.0f + expf(-b));
+        }
+    }
+}
+
+constexpr int kScanWarps = 4, kScanCols = 4, kScanBlockCols = kScanWarps * kScanCols;
+
+template <typename T, int R>
+__global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan_kernel(const float* qf, const float* kf, const float* gates, const T* proj,
+                                                                          int ld, float* obuf, float* state, long long state_stride,
+                                                                          const int* segment_info, RecurrenceSpec s, int batch) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    const size_t stage = static_cast<size_t>(batch) * s.dim;
+    float* qs = reinterpret_cast<float*>(smem);                // [2][batch][dim]: a batch is copied while the one before is walked
+    float* ks = qs + 2 * stage;                                // [2][batch][dim]
+    float* vs = ks + 2 * stage;                                // [batch][16]
+    float* os = vs + static_cast<size_t>(batch) * kScanBlockCols;   // [batch][16]
+    float* gs = os + static_cast<size_t>(batch) * kScanBlockCols;   // [batch]
+    float* bs = gs + batch;                                    // [batch]
+    const int segment = blockIdx.x, head = blockIdx.y, block_col = blockIdx.z * kScanBlockCols;
+    const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], slot = segment_info[4 * segment + 3];
+    const int qk_head = head / (s.heads / s.qk_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = block_col + warp * kScanCols;
+    const size_t qk_ld = static_cast<size_t>(s.qk_heads) * s.dim;
+    const size_t o_ld = static_cast<size_t>(s.heads) * s.vdim;
+    const bool wide = s.dim % 4 == 0;                          // rows of q and k start on 16-byte borders
+
+    float S[kScanCols][R];
+    float* my_state = state + static_cast<size_t>(slot) * state_stride + (static_cast<size_t>(head) * s.vdim) * s.dim;
+#pragma unroll
+    for (int c = 0; c < kScanCols; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = lane + 32 * r;
+            S[c][r] = (col0 + c < s.vdim && d < s.dim) ? my_state[static_cast<size_t>(col0 + c) * s.dim + d] : 0.0f;
+        }
+    const float decay = s.rule == 0 ? s.decay[head] : 1.0f;
+
+    constexpr int kVPerThread = 32 * kScanBlockCols / (kScanWarps * 32);     // batch <= 32
+    float v_next[kVPerThread], g_next = 0.0f, b_next = 0.0f;
+    // Starts the copies of a batch's q and k into a stage and loads its v, g and beta into registers.
+    auto fetch = [&](int base, int into) {
+        const int n = min(batch, count - base);
+        const float* qsrc = qf + static_cast<size_t>(first + base) * qk_ld + static_cast<size_t>(qk_head) * s.dim;
+        const float* ksrc = kf + static_cast<size_t>(first + base) * qk_ld + static_cast<size_t>(qk_head) * s.dim;
+        float* qdst = qs + into * stage;
+        float* kdst = ks + into * stage;
+        if (wide) {
+            const int per_row = s.dim / 4;
+            for (int i = threadIdx.x; i < n * per_row; i += blockDim.x) {
+                const int t = i / per_row, c = (i % per_row) * 4;
+                mlr_async_copy16(qdst + static_cast<size_t>(t) * s.dim + c, qsrc + t * qk_ld + c);
+                mlr_async_copy16(kdst + static_cast<size_t>(t) * s.dim + c, ksrc + t * qk_ld + c);
+            }
+        } else {
+            for (int i = threadIdx.x; i < n * s.dim; i += blockDim.x) {
+                const int t = i / s.dim, c = i % s.dim;
+                mlr_async_copy4(qdst + static_cast<size_t>(t) * s.dim + c, qsrc + t * qk_ld + c);
+                mlr_async_copy4(kdst + static_cast<size_t>(t) * s.dim + c, ksrc + t * qk_ld + c);
+            }
+        }
+        mlr_async_commit();
+#pragma unroll
+        for (int j = 0; j < kVPerThread; ++j) {
+            const int i = threadIdx.x + j * kScanWarps * 32;
+            const int t = i / kScanBlockCols, c = block_col + i % kScanBlockCols;
+            v_next[j] = (t < n && c < s.vdim) ? mlr_load(proj + static_cast<size_t>(first + base + t) * ld, s.col_v + head * s.vdim + c) : 0.0f;
+        }
+        if (s.rule == 1 && threadIdx.x < n) {
+            g_next = __ldcg(gates + static_cast<size_t>(first + base + threadIdx.x) * 2 * s.heads + head);
+            b_next = __ldcg(gates + static_cast<size_t>(first + base + threadIdx.x) * 2 * s.heads + s.heads + head);
+        }
+    };
+
+    fetch(0, 0);
+    int current = 0;
+    for (int base = 0; base < count; base += batch, current ^= 1) {
+        const int n = min(batch, count - base);
+        __syncthreads();                    // the batch before has been walked and written out
+#pragma unroll
+        for (int j = 0; j < kVPerThread; ++j) {
+            const int i = threadIdx.x + j * kScanWarps * 32;
+            if (i < batch * kScanBlockCols) vs[i] = v_next[j];
+        }
+        if (threadIdx.x < batch) {
+            gs[threadIdx.x] = g_next;
+            bs[threadIdx.x] = b_next;
+        }
+        mlr_async_wait();
+        __syncthreads();
+        if (base + batch < count) fetch(base + batch, current ^ 1);
+        const float* qnow = qs + current * stage;
+        const float* know = ks + current * stage;
+        for (int t = 0; t < n; ++t) {
+            float kk[R], qq[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int d = lane + 32 * r;
+                kk[r] = d < s.dim ? know[static_cast<size_t>(t) * s.dim + d] : 0.0f;
+                qq[r] = d < s.dim ? qnow[static_cast<size_t>(t) * s.dim + d] : 0.0f;
+            }
+            float o[kScanCols];
+            if (s.rule == 0) {
+#pragma unroll
+                for (int c = 0; c < kScanCols; ++c) {
+                    const float v = vs[t * kScanBlockCols + warp * kScanCols + c];
+                    float dot = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        S[c][r] = fmaf(decay, S[c][r], kk[r] * v);
+                        dot = fmaf(S[c][r], qq[r], dot);
+                    }
+                    o[c] = dot;
+                }
+            } else {
+                const float g = gs[t], beta = bs[t];
+                float dotk[kScanCols];
+#pragma unroll
+                for (int c = 0; c < kScanCols; ++c) {
+                    float dot = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        S[c][r] *= g;
+                        dot = fmaf(S[c][r], kk[r], dot);
+                    }
+                    dotk[c] = dot;
+                }
+#pragma unroll
+                for (int c = 0; c < kScanCols; ++c) dotk[c] = mlr_warp_sum(dotk[c]);
+#pragma unroll
+                for (int c = 0; c < kScanCols; ++c) {
+                    const float v = vs[t * kScanBlockCols + warp * kScanCols + c];
+                    const float u = beta * (v - dotk[c]);
+                    float dot = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        S[c][r] = fmaf(kk[r], u, S[c][r]);
+                        dot = fmaf(S[c][r], qq[r], dot);
+                    }
+                    o[c] = dot;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < kScanCols; ++c) o[c] = mlr_warp_sum(o[c]);
+            if (lane == 0) {
+#pragma unroll
+                for (int c = 0; c < kScanCols; ++c) os[t * kScanBlockCols + warp * kScanCols + c] = o[c];
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * kScanBlockCols; i += blockDim.x) {
+            const int t = i / kScanBlockCols, c = block_col + i % kScanBlockCols;
+            if (c < s.vdim) obuf[static_cast<size_t>(first + base + t) * o_ld + static_cast<size_t>(head) * s.vdim + c] = os[i];
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kScanCols; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int d = lane + 32 * r;
+            if (col0 + c < s.vdim && d < s.dim) my_state[static_cast<size_t>(col0 + c) * s.dim + d] = S[c][r];
+        }
+}
+
+// Norm per head, weight, gate and the constant on the scan's float32 outputs [rows, heads * vdim].
+template <typename T>
+__global__ void __launch_bounds__(128) recurrence_readout_kernel(const float* obuf, const T* side, int ld_side, T* out, int ld_out,
+                                                                 RecurrenceSpec s) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int head = warp; head < s.heads; head += warps) {
+        const float* o = obuf + (static_cast<size_t>(row) * s.heads + head) * s.vdim;
+        float inv = 1.0f;
+        if (s.eps >= 0.0f) {
+            float sum = 0.0f;
+            for (int c = lane; c < s.vdim; c += 32) {
+                const float v = __ldcg(o + c);
+                sum = fmaf(v, v, sum);
+            }
+            inv = 1.0f / sqrtf(mlr_warp_sum(sum) / static_cast<float>(s.vdim) + s.eps);
+        }
+        const T* grow = side + static_cast<size_t>(row) * ld_side;
+        T* orow = out + static_cast<size_t>(row) * ld_out + static_cast<size_t>(head) * s.vdim;
+        for (int c = lane; c < s.vdim; c += 32) {
+            float value = __ldcg(o + c) * inv;
+            if (s.out_weight) value *= s.out_weight[c];
+            if (s.gate_kind) {
+                const float g = mlr_load(grow, s.col_gate + head * s.vdim + c);
+                const float sig = 1.0f / (1.0f + expf(-g));
+                value *= s.gate_kind == 2 ? g * sig : sig;
+            }
+            mlr_store(orow, c, value * s.out_scale);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) short_conv_kernel(const T* in, int ld_in, T* out, int ld_out, int channels, int taps,
                                                          const float* weights, const float* state, long long state_stride,
@@ -319,6 +569,56 @@ MLR_API int mlr_linear_recurrence(const RecurrenceSpec* spec, const void* proj, 
 #undef MLR_PICK
 #undef MLR_GO
     return mlr_launched("linear_recurrence");
+}
+
+static int check_recurrence(const RecurrenceSpec& s) {
+    MLR_REQUIRE(s.heads > 0 && s.qk_heads > 0 && s.heads % s.qk_heads == 0 && s.heads <= 65535,
+                "linear_recurrence: %d heads cannot share %d q/k heads", s.heads, s.qk_heads);
+    MLR_REQUIRE(s.dim >= 1 && s.dim <= 256 && s.vdim >= 1 && s.vdim <= 256 && !(s.dim > 128 && s.vdim > 128),
+                "linear_recurrence: a state of %d x %d per head is more than a block's registers hold (256 x 128 or 128 x 256)", s.dim, s.vdim);
+    MLR_REQUIRE(s.prep != 1 || (s.rot_dims >= 0 && s.rot_dims % 2 == 0 && s.rot_dims <= s.dim && (s.rot_dims == 0 || s.freq)),
+                "linear_recurrence: %d rotated values do not fit a head of %d", s.rot_dims, s.dim);
+    MLR_REQUIRE(s.rule == 0 ? s.decay != nullptr : (s.rule == 1 && s.a_log && s.dt_bias), "linear_recurrence: the rule's constants are missing");
+    return 0;
+}
+
+// The three-kernel form.  qf, kf: float32 [rows, qk_heads * dim]; gates: float32 [rows, 2 * heads] (delta rule; else unused);
+// obuf: float32 [rows, heads * vdim].  Same results as `mlr_linear_recurrence` up to the order of no sum: both add in the same order.
+MLR_API int mlr_linear_recurrence_split(const RecurrenceSpec* spec, const void* proj, int ld, const void* side, int ld_side, int act_bf16,
+                                        void* out, int ld_out, float* state, long long state_stride, const int* segment_info,
+                                        int n_segments, const int* positions, int rows, float* qf, float* kf, float* gates, float* obuf,
+                                        cudaStream_t stream) {
+    MLR_REQUIRE(spec, "linear_recurrence_split: no description");
+    const RecurrenceSpec& s = *spec;
+    if (check_recurrence(s)) return 1;
+    MLR_REQUIRE(n_segments >= 0 && rows >= 0 && state && proj && side && out && qf && kf && obuf && positions && (s.rule == 0 || gates),
+                "linear_recurrence_split: bad arguments");
+    if (n_segments == 0 || rows == 0) return 0;
+    const int regs = s.dim <= 32 ? 1 : s.dim <= 64 ? 2 : s.dim <= 128 ? 4 : 8;
+    const size_t per_token = sizeof(float) * (4 * static_cast<size_t>(s.dim) + 2 * kScanBlockCols + 2);    // q and k in two stages
+    int batch = static_cast<int>((44 * 1024) / per_token);
+    batch = batch < 1 ? 1 : (batch > 32 ? 32 : batch);
+    const size_t shared = per_token * batch;
+    const dim3 grid(n_segments, s.heads, (s.vdim + kScanBlockCols - 1) / kScanBlockCols);
+#define MLR_SPLIT(T)                                                                                                                   \
+    do {                                                                                                                               \
+        mlr_launch((recurrence_prepare_kernel<T>), dim3(rows), dim3(128), 0, stream, static_cast<const T*>(proj), ld,                  \
+                   static_cast<const T*>(side), ld_side, qf, kf, gates, positions, s);                                                 \
+        if (regs == 1) mlr_launch((recurrence_scan_kernel<T, 1>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates,    \
+                                  static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch);                 \
+        else if (regs == 2) mlr_launch((recurrence_scan_kernel<T, 2>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates, \
+                                       static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch);            \
+        else if (regs == 4) mlr_launch((recurrence_scan_kernel<T, 4>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates, \
+                                       static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch);            \
+        else mlr_launch((recurrence_scan_kernel<T, 8>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates,              \
+                        static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch);                           \
+        mlr_launch((recurrence_readout_kernel<T>), dim3(rows), dim3(128), 0, stream, obuf, static_cast<const T*>(side), ld_side,       \
+                   static_cast<T*>(out), ld_out, s);                                                                                   \
+    } while (0)
+    if (act_bf16) MLR_SPLIT(__nv_bfloat16);
+    else MLR_SPLIT(float);
+#undef MLR_SPLIT
+    return mlr_launched("linear_recurrence_split");
 }
 
 MLR_API int mlr_short_conv(const void* in, int ld_in, void* out, int ld_out, int act_bf16, int channels, int taps,

@@ -60,7 +60,7 @@ def _give_library_workspace(device: torch.device) -> None:
 
 
 _ROUTING = {"gemv_rows", "gemv_balance", "fuse_rotation_rows", "use_tcgen05", "tcgen05_prefill", "pair_rows", "pair_everything", "tcgen05_attention", "decode_rows",
-            "own_activation_products", "pair_min_tiles"}
+            "own_activation_products", "pair_min_tiles", "recurrence_fused_rows"}
 
 
 def units_balance(rows: int, sm_count: int) -> float:
@@ -123,6 +123,11 @@ class Runtime:
         # step of the 8B sizes (8 layers, context 2000): 0.867 ms against 0.884 ms at one request, 1.169 against 1.187 ms
         # at 16, but 1.700 against 1.660 ms at 64, where every one of many more blocks repeats the work on its queries.
         self.fuse_rotation_rows = 32
+        # A mixer with a matrix state per head runs steps of up to this many rows in ONE kernel with a block per (request,
+        # head); larger steps (prompt portions) as prepare / scan / read-out, where the scan has a block per (request,
+        # head, 16 columns of the state) and the rest is parallel over rows.  Measured at 2048 rows of one request, 8 heads
+        # of 128 x 128: 2.55 ms in the one kernel; decode steps of 8 rows: 11 us, and three launches would cost more.
+        self.recurrence_fused_rows = 64
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.shared_memory_limit = torch.cuda.get_device_properties(self.device).shared_memory_per_block_optin
         if dtype is torch.bfloat16:

@@ -99,6 +99,8 @@ _SIGNATURES = {
     "recurrence": {
         "mlr_linear_recurrence": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
                                   c_int, c_void_p, c_void_p],
+        "mlr_linear_recurrence_split": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
+                                        c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "mlr_short_conv": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                            c_int, c_void_p],
         "mlr_short_conv_state": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p],

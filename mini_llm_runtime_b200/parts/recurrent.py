@@ -27,6 +27,24 @@ from ..weights.loader import WeightSpec
 from .base import RunContext, SequenceCore, StateNeed, columns_of
 
 
+def emit_recurrence(b, mixer, proj, side, act, run: RunContext) -> None:
+    """The recurrence of `mixer.desc` over the step's rows: q, k, v from `proj`, the rule's inputs and the gate
+    from `side`, the result into `act`.  Few rows: one kernel.  Many: prepare, scan, read-out."""
+    state, info = run.state, b.meta("segment_info")
+    if b.le(proj.rows, b.rt.recurrence_fused_rows):
+        b.launch("recurrence", "mlr_linear_recurrence", address(mixer.desc), proj.ptr, proj.ld, side.ptr, side.ld, proj.is_bf16,
+                 act.ptr, act.ld, state.data_ptr(), state.stride(0), info, b.segments, b.status, b.stream)
+        return
+    d = mixer.desc
+    qf = b.temp(proj.rows, d.qk_heads * d.dim, torch.float32)
+    kf = b.temp(proj.rows, d.qk_heads * d.dim, torch.float32)
+    gates = b.temp(proj.rows, 2 * d.heads, torch.float32)
+    obuf = b.temp(proj.rows, d.heads * d.vdim, torch.float32)
+    b.launch("recurrence", "mlr_linear_recurrence_split", address(d), proj.ptr, proj.ld, side.ptr, side.ld, proj.is_bf16, act.ptr,
+             act.ld, state.data_ptr(), state.stride(0), info, b.segments, b.meta("positions"), proj.rows, qf.ptr, kf.ptr, gates.ptr,
+             obuf.ptr, b.stream)
+
+
 def _check_state_size(dim: int, vdim: int) -> None:
     if not (1 <= dim <= 256 and 1 <= vdim <= 256) or (dim > 128 and vdim > 128):
         raise ConfigError(f"a state of {dim} x {vdim} per head is more than the recurrence kernel keeps in registers "
@@ -85,8 +103,7 @@ class RetentionMixer(SequenceCore):
             unit_eps=0.0, eps=self.eps, out_scale=float(out_scale))
 
     def emit_core(self, b, proj, act, run: RunContext) -> None:
-        b.launch("recurrence", "mlr_linear_recurrence", address(self.desc), proj.ptr, proj.ld, proj.ptr, proj.ld, proj.is_bf16,
-                 act.ptr, act.ld, run.state.data_ptr(), run.state.stride(0), b.meta("segment_info"), b.segments, b.status, b.stream)
+        emit_recurrence(b, self, proj, proj, act, run)
 
 
 class DeltaRuleMixer(SequenceCore):
@@ -160,8 +177,7 @@ class DeltaRuleMixer(SequenceCore):
                  self.taps_weight.data_ptr(), conv_state, stride, info, of_row, proj.rows, b.stream)
         b.launch("recurrence", "mlr_short_conv_state", proj.ptr, proj.ld, proj.is_bf16, self.channels, self.taps, conv_state, stride,
                  info, b.segments, b.stream)
-        b.launch("recurrence", "mlr_linear_recurrence", address(self.desc), conv.ptr, conv.ld, proj.ptr, proj.ld, proj.is_bf16,
-                 act.ptr, act.ld, state.data_ptr(), stride, info, b.segments, b.status, b.stream)
+        emit_recurrence(b, self, conv, proj, act, run)
 
 
 register_part("mixer", "retention", RetentionMixer)

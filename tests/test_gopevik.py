@@ -289,7 +289,7 @@ def test_a_loud_key_just_inside_and_just_outside_the_chunk(chunk, T):
         assert torch.allclose(got, want, atol=2e-5, rtol=2e-5), (key, float((got - want).abs().max()))
 
 
-def _recurrence_case(dtype, rule, heads, qk_heads, dim, vdim, rot_dims, segments, slots=4, taps=0, seed=0, weight=True, gate="silu"):
+def _recurrence_case(dtype, rule, heads, qk_heads, dim, vdim, rot_dims, segments, slots=4, taps=0, seed=0, weight=True, gate="silu", split=False):
     """`segments`: token counts of requests that share one launch; each request then runs a second step
     of 1 token (its state carried in its slot).  Returns engine and plain outputs for all rows of both steps."""
     from mini_llm_runtime_b200.ops import native
@@ -325,9 +325,19 @@ def _recurrence_case(dtype, rule, heads, qk_heads, dim, vdim, rot_dims, segments
         proj = torch.cat(rows).to(dtype).to(dev)
         _, _, seg_info = _meta(info, dev)
         out = torch.empty(proj.shape[0], heads * vdim, dtype=dtype, device=dev)
-        _call("recurrence", "mlr_linear_recurrence", ctypes.addressof(spec), proj.data_ptr(), proj.stride(0), proj.data_ptr(),
-              proj.stride(0), native.is_bf16(proj), out.data_ptr(), out.stride(0), state.data_ptr(), state.stride(0),
-              seg_info.data_ptr(), len(segments), None, native.stream())
+        if split and part == 0:      # the first step in three kernels, the second (one token each) in the fused one
+            rows = proj.shape[0]
+            positions, _, _ = _meta(info, dev)
+            qf, kf = (torch.empty(rows, qk_heads * dim, device=dev) for _ in range(2))
+            gb, obuf = torch.empty(rows, 2 * heads, device=dev), torch.empty(rows, heads * vdim, device=dev)
+            _call("recurrence", "mlr_linear_recurrence_split", ctypes.addressof(spec), proj.data_ptr(), proj.stride(0), proj.data_ptr(),
+                  proj.stride(0), native.is_bf16(proj), out.data_ptr(), out.stride(0), state.data_ptr(), state.stride(0),
+                  seg_info.data_ptr(), len(segments), positions.data_ptr(), rows, qf.data_ptr(), kf.data_ptr(), gb.data_ptr(),
+                  obuf.data_ptr(), native.stream())
+        else:
+            _call("recurrence", "mlr_linear_recurrence", ctypes.addressof(spec), proj.data_ptr(), proj.stride(0), proj.data_ptr(),
+                  proj.stride(0), native.is_bf16(proj), out.data_ptr(), out.stride(0), state.data_ptr(), state.stride(0),
+                  seg_info.data_ptr(), len(segments), None, native.stream())
         for i, (f, c, _, _) in enumerate(info):
             got[i].append(out[f:f + c].float().cpu().double())
     wants = []
@@ -367,11 +377,16 @@ def _recurrence_case(dtype, rule, heads, qk_heads, dim, vdim, rot_dims, segments
     dict(rule="delta", heads=2, qk_heads=2, dim=64, vdim=200, rot_dims=0, segments=[40]),
     dict(rule="delta", heads=6, qk_heads=1, dim=8, vdim=33, rot_dims=0, segments=[2, 65]),
 ])
-def test_recurrence_kernel_with_state_carried_between_steps(dtype, case):
-    got, want = _recurrence_case(dtype, **case)
+@pytest.mark.parametrize("split", [False, True])
+def test_recurrence_kernel_with_state_carried_between_steps(dtype, case, split):
+    got, want = _recurrence_case(dtype, split=split, **case)
     tol = 3e-5 if dtype is torch.float32 else 4e-2
     for i, (a, b) in enumerate(zip(got, want)):
         assert torch.allclose(a, b, atol=tol, rtol=tol), (i, float((a - b).abs().max()))
+    if split:       # prepare / scan / read-out add in the order of the one kernel: the same bits
+        fused, _ = _recurrence_case(dtype, split=False, **case)
+        for a, b in zip(got, fused):
+            assert torch.equal(a, b)
 
 
 @pytest.mark.gpu
@@ -438,7 +453,7 @@ def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation
     want = plain_logits(config, weights, tokens)
     whole = run_whole(model, tokens)
     close(whole, want, dtype, "whole")
-    for sizes in ([1], [2], [3, 2, 7], [64, 1], [149, 1], [11, 2, 2, 30, 1, 5]):      # [1]: decoding from the first token on
+    for sizes in ([1], [2], [3, 2, 7], [64, 1], [65, 2, 70], [149, 1], [11, 2, 2, 30, 1, 5]):      # [1]: decoding from the first token on
         got = run_portions(model, tokens, sizes)
         close(got, want, dtype, f"portions {sizes}")
         if dtype == "float32":      # how a prompt is cut changes nothing but the order of a few sums
