@@ -281,6 +281,96 @@ def serving(args, cfg, model, prompt_of, gen) -> int:
     return 0
 
 
+# ---- `--compare gopevik`: the Gopevik design beside the dense Qwen3 decoder at equal layer sizes (random weights) ----
+# (name, width, feed-forward, query heads, kv heads, head size): the layer sizes of a 1.7B and of an 8B dense model.
+COMPARE_SIZES = [("w2048", 2048, 6144, 16, 8, 128), ("w4096", 4096, 12288, 32, 8, 128)]
+
+
+def gopevik_config(width, ff, heads, kv, dim, layers, chunk, vocab):
+    """Three layers with the two mixers side by side (attention in chunks of `chunk` positions beside retention) to one
+    with the delta rule, all with a feed-forward: per layer about 1.25 x the matrix parameters of the Qwen3 layer."""
+    side = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff}, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": chunk},
+                 "rot": {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 4.0}}},
+        "right": {"heads": heads // 2, "dim": dim, "vdim": dim, "decay": [1 - 2.0 ** (-5 - i % 4) for i in range(heads // 2)],
+                  "rot": {"base": 1e4, "dims": dim}},
+        "left_scale": 0.8, "right_scale": 0.9}}
+    delta = {"type": "delta", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": dim, "vdim": dim, "conv": 4}}
+    return {"architecture": "Gopevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "layers": [(side, side, delta, side)[i % 4] for i in range(layers)]}
+
+
+def compare_designs(args) -> int:
+    """Prefill (one request of `--context` tokens in one step) and decode (`--batch` requests at that context, one token
+    each a step, replayed from CUDA graphs) of both designs, `--layers` layers each (default 4), timed with CUDA events
+    after warm-up; every timed step reads its weights (hundreds of MB) anew, far more than L2 keeps."""
+    import torch
+    from mini_llm_runtime_b200.engine.loading import random_model
+    from mini_llm_runtime_b200.engine.model import CacheConfig, StepEntry
+    layers, context, batch, vocab = args.layers or 4, args.context or 2048, args.batch, 32000
+    steps, warmup = args.steps, max(args.warmup, 5)
+
+    def measure(cfg):
+        pages = (batch + 1) * ((context + 64) // args.page_size + 1)
+        model = random_model(cfg, seed=1, dtype="bfloat16", cache=CacheConfig(page_size=args.page_size, num_pages=pages, max_requests=batch + 1,
+                                                                             max_model_len=context + 64))
+        gen = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, vocab, (context,), generator=gen).tolist()
+        times = []
+        for _ in range(3 + 5):
+            slot = model.open_request()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            model.step([StepEntry(slot, prompt, [context - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            model.close_request(slot)
+        prefill_ms = statistics.median(times[3:])
+        slots = [model.open_request() for _ in range(batch)]
+        for slot in slots:
+            model.step([StepEntry(slot, prompt[:context - 1 - steps - warmup], [])])
+        entries = [StepEntry(slot, [7], [0]) for slot in slots]
+        for _ in range(warmup):
+            model.step(entries)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            model.step(entries)
+        b.record()
+        torch.cuda.synchronize()
+        model.check_status()
+        decode_ms = a.elapsed_time(b) / steps
+        params = 0
+        for spec in model.expected_weights().values():
+            count = 1
+            for extent in spec.shape:
+                count *= extent
+            params += count
+        out = {"prefill_tokens_per_s": context / prefill_ms * 1e3, "prefill_ms": prefill_ms, "decode_tokens_per_s": batch / decode_ms * 1e3,
+               "decode_ms_per_step": decode_ms, "parameters": params, "graphs": len(model._graphs)}
+        del model
+        torch.cuda.empty_cache()
+        return out
+
+    results = {}
+    with ClockSampler() as clocks:
+        for name, width, ff, heads, kv, dim in COMPARE_SIZES:
+            qwen = dict(QWEN3_8B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv,
+                        head_dim=dim, intermediate_size=ff, vocab_size=vocab)
+            g = measure(gopevik_config(width, ff, heads, kv, dim, layers, context, vocab))
+            q = measure(qwen)
+            results[name] = {"gopevik": g, "qwen3": q,
+                             "prefill_ratio": g["prefill_tokens_per_s"] / q["prefill_tokens_per_s"],
+                             "decode_ratio": g["decode_tokens_per_s"] / q["decode_tokens_per_s"]}
+    print(json.dumps({"metric": "prefill and decode tok/s of the Gopevik design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
+                      "layers": layers, "context": context, "batch": batch, "steps": steps, "warmup": warmup, "dtype": "bf16",
+                      "data": "synthetic", "sizes": results, "clocks": clocks.summary()}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -301,12 +391,17 @@ def main() -> int:
                     help="every matrix product on the package's tcgen05 kernel, none on the vendor library (slower)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the baseline's configuration has 16; 64 is a little faster)")
     ap.add_argument("--no-check", action="store_true", help="skip the agreement check of bfloat16 and float32 before the measurement")
+    ap.add_argument("--compare", default=None, choices=["gopevik"],
+                    help="instead of the headline: prefill and decode of the named design beside Qwen3 at equal layer sizes "
+                         "(--layers layers, default 4; --context, default 2048; --batch); prints one JSON line of its own")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.compare:
+        return compare_designs(args)
     if args.warmup < 5:
         args.warmup = 5      # a decode shape is captured into a graph on its third step, and the first step may end a context bucket
 

@@ -19,7 +19,7 @@ from typing import Any, Dict, Optional, Tuple
 from .base import ConfigError
 
 _LIMIT = 1_000_000
-MAX_POSITIONS = 1 << 20
+MAX_POSITIONS = 1 << 17
 
 
 def _get(raw: dict, key: str, where: str):

@@ -79,7 +79,8 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
                                                                     const T* cache, int num_pages, const int* positions,
                                                                     const int* segment_of_row, const int* block_table,
                                                                     int table_stride, int page_size, MaskedAttentionSpec s,
-                                                                    const int* items, const int* segment_info, int* status) {
+                                                                    const int* items, const int* segment_info, int split_keys,
+                                                                    int max_splits, float* partial, int* status) {
     mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -123,16 +124,54 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     if (threadIdx.x == 0) bad = 0;
     __syncthreads();
 
-    // The sink is a key of score 0 that is always seen and carries no value.
-    float running_max = s.sink ? 0.0f : -INFINITY, running_sum = s.sink ? 1.0f : 0.0f;
+    // The sink is a key of score 0 that is always seen and carries no value.  With `partial` the visible keys are cut
+    // into ranges of `split_keys` (from the 64-key border at or below the first one); blockIdx.z names this block's
+    // range, whose maximum, sum and weighted values go to `partial` for `attention_masked_merge_kernel` (the sink too).
+    float running_max = (s.sink && !partial) ? 0.0f : -INFINITY, running_sum = (s.sink && !partial) ? 1.0f : 0.0f;
     float acc[kMaxDimsPerThread] = {0.0f, 0.0f};
+    int tile_first = (lo / kTile) * kTile, tile_last = position;
+    if (partial) {
+        tile_first += blockIdx.z * split_keys;
+        tile_last = min(position, tile_first + split_keys - 1);
+        if (tile_first > position) return;           // the merge reads only the ranges that exist for this row
+    }
 
-    for (int tile = (lo / kTile) * kTile; tile <= position; tile += kTile) {
+    constexpr int kChunk = 16 / sizeof(T);                      // values in 16 bytes
+    const bool chunked_rows = s.dim % kChunk == 0;              // a key's row is whole 16-byte pieces, each aligned
+    for (int tile = tile_first; tile <= tile_last; tile += kTile) {
+        if (chunked_rows) {
+            // Scores of this tile: two threads per key, each adds up every other 16-byte piece of the key's row.
+            const int i = threadIdx.x >> 1, t = tile + i;
+            float partial = 0.0f;
+            long long offset = -1;
+            if (t >= lo && t <= tile_last) {
+                const int page = table[t / page_size];
+                if (page < 0 || page >= num_pages) {
+                    bad = 1;
+                } else {
+                    const T* k = cache + page * page_elems + (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.dim;
+                    offset = static_cast<long long>(page * page_elems + key_plane +
+                                                    (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.vdim);
+                    for (int c = (threadIdx.x & 1) * kChunk; c < s.dim; c += 2 * kChunk) {
+                        float v[kChunk];
+                        if constexpr (sizeof(T) == 2) mlr_load8(k + c, v);
+                        else mlr_load4(k + c, v);
+#pragma unroll
+                        for (int e = 0; e < kChunk; ++e) partial = fmaf(qs[c + e], v[e], partial);
+                    }
+                }
+            }
+            partial += __shfl_xor_sync(0xffffffffu, partial, 1);
+            if ((threadIdx.x & 1) == 0) {
+                scores[i] = offset >= 0 ? partial * s.scale : -INFINITY;
+                offsets[i] = offset;
+            }
+        } else
         for (int i = warp; i < kTile; i += kThreads / 32) {
             const int t = tile + i;
             float score = -INFINITY;
             long long offset = -1;
-            if (t >= lo && t <= position) {
+            if (t >= lo && t <= tile_last) {
                 const int page = table[t / page_size];
                 if (page < 0 || page >= num_pages) {
                     if (lane == 0) bad = 1;
@@ -182,6 +221,21 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
         __syncthreads();
     }
     if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
+    if (partial) {
+        const int j = blockIdx.x % kRowsPerItem;
+        float* mine = partial + ((static_cast<size_t>(blockIdx.x / kRowsPerItem) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits +
+                                 blockIdx.z) * (s.vdim + 2);
+        if (threadIdx.x == 0) {
+            mine[0] = running_max;
+            mine[1] = running_sum;
+        }
+#pragma unroll
+        for (int d = 0; d < kMaxDimsPerThread; ++d) {
+            const int c = threadIdx.x + d * kThreads;
+            if (c < s.vdim) mine[2 + c] = acc[d];
+        }
+        return;
+    }
     T* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
     const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * s.vdim : nullptr;
 #pragma unroll
@@ -189,6 +243,56 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
         const int c = threadIdx.x + d * kThreads;
         if (c < s.vdim) {
             float value = running_sum > 0.0f ? acc[d] / running_sum : 0.0f;
+            if (grow) {
+                const float g = mlr_load(grow, c);
+                const float sig = 1.0f / (1.0f + expf(-g));
+                value *= s.gate_kind == 2 ? g * sig : sig;
+            }
+            mlr_store(orow, c, value * s.out_scale);
+        }
+    }
+}
+
+// Adds up the key ranges of a row: grid (segments of few rows * 16, heads), as the row kernel's.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const float* partial, const T* gate, int ld_gate, T* out, int ldo,
+                                                                          const int* positions, MaskedAttentionSpec s, const int* items,
+                                                                          const int* segment_info, int split_keys, int max_splits) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    const int item = blockIdx.x / kRowsPerItem, j = blockIdx.x % kRowsPerItem, head = blockIdx.y;
+    const int* info = segment_info + 4 * (items ? items[item] : item);
+    if (j >= info[1]) return;
+    const int row = info[0] + j;
+    const int position = positions[row];
+    int lo = 0;
+    if (s.window > 0) lo = max(lo, position - s.window + 1);
+    if (s.chunk > 0) lo = max(lo, (position / s.chunk) * s.chunk);
+    const int splits = (position - (lo / kTile) * kTile) / split_keys + 1;
+    const float* mine = partial + (static_cast<size_t>(item) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits * (s.vdim + 2);
+    float top = s.sink ? 0.0f : -INFINITY;
+    for (int i = 0; i < splits; ++i) top = fmaxf(top, __ldcg(mine + static_cast<size_t>(i) * (s.vdim + 2)));
+    float sum = s.sink ? expf(-top) : 0.0f;
+    float acc[kMaxDimsPerThread] = {0.0f, 0.0f};
+    for (int i = 0; i < splits; ++i) {
+        const float* part = mine + static_cast<size_t>(i) * (s.vdim + 2);
+        const float m = __ldcg(part);
+        if (m == -INFINITY) continue;
+        const float w = expf(m - top);
+        sum = fmaf(__ldcg(part + 1), w, sum);
+#pragma unroll
+        for (int d = 0; d < kMaxDimsPerThread; ++d) {
+            const int c = threadIdx.x + d * kThreads;
+            if (c < s.vdim) acc[d] = fmaf(__ldcg(part + 2 + c), w, acc[d]);
+        }
+    }
+    T* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
+    const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * s.vdim : nullptr;
+#pragma unroll
+    for (int d = 0; d < kMaxDimsPerThread; ++d) {
+        const int c = threadIdx.x + d * kThreads;
+        if (c < s.vdim) {
+            float value = sum > 0.0f ? acc[d] / sum : 0.0f;
             if (grow) {
                 const float g = mlr_load(grow, c);
                 const float sig = 1.0f / (1.0f + expf(-g));
@@ -453,26 +557,49 @@ MLR_API int mlr_kv_rope_cache(const MaskedAttentionSpec* spec, const void* k, in
 MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q, int ldq, const void* gate, int ld_gate, void* out,
                                  int ldo, int act_bf16, const void* cache, int num_pages, const int* positions,
                                  const int* segment_of_row, const int* block_table, int table_stride, int page_size, int rows,
-                                 const int* items, int n_items, const int* segment_info, int* status, cudaStream_t stream) {
+                                 const int* items, int n_items, const int* segment_info, int split_keys, int max_splits,
+                                 float* partial, int* status, cudaStream_t stream) {
     // With `segment_info` the kernel runs over `n_items` segments of at most 16 rows each (`items` lists them; null: the
-    // step's first n_items segments) and `rows` is not used; without it, over all `rows` rows.
+    // step's first n_items segments) and `rows` is not used; without it, over all `rows` rows.  With `partial` (float32,
+    // n_items * 16 * kv_heads * max_splits * (vdim + 2), segments of at most 16 / (heads / kv_heads) rows) and more than
+    // one split, every row's keys are cut into ranges of `split_keys` that run as blocks of their own, and a second
+    // kernel adds the ranges up.
     if (check_spec(spec, "attention_masked")) return 1;
     if (segment_info) rows = n_items * kRowsPerItem;
+    if (!partial || max_splits <= 1 || !segment_info) {
+        partial = nullptr;
+        max_splits = 1;
+    } else {
+        MLR_REQUIRE(split_keys >= kTile && split_keys % kTile == 0 && max_splits <= 65535, "attention_masked: bad key split %d x %d",
+                    split_keys, max_splits);
+    }
     MLR_REQUIRE(rows >= 0 && page_size > 0 && num_pages > 0, "attention_masked: bad page size or page count");
     MLR_REQUIRE(ldq >= spec->heads * spec->dim && ldo >= spec->heads * spec->vdim, "attention_masked: a row stride is smaller than the row");
     MLR_REQUIRE((spec->gate_kind == 0) == (gate == nullptr), "attention_masked: the description and the call disagree about a gate");
     if (rows == 0) return 0;
     const size_t shared = sizeof(float) * (spec->dim + kTile) + sizeof(long long) * kTile + 16;
-    const dim3 grid(rows, spec->heads);
+    const dim3 grid(rows, spec->heads, max_splits);
+    const dim3 merge_grid(rows, spec->heads);
     if (act_bf16)
         mlr_launch((attention_masked_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream,
                    static_cast<const __nv_bfloat16*>(q), ldq, static_cast<const __nv_bfloat16*>(gate), ld_gate,
                    static_cast<__nv_bfloat16*>(out), ldo, static_cast<const __nv_bfloat16*>(cache), num_pages, positions, segment_of_row,
-                   block_table, table_stride, page_size, *spec, items, segment_info, status);
+                   block_table, table_stride, page_size, *spec, items, segment_info, split_keys, max_splits, partial, status);
     else
         mlr_launch((attention_masked_kernel<float>), dim3(grid), dim3(kThreads), shared, stream, static_cast<const float*>(q), ldq,
                    static_cast<const float*>(gate), ld_gate, static_cast<float*>(out), ldo, static_cast<const float*>(cache), num_pages,
-                   positions, segment_of_row, block_table, table_stride, page_size, *spec, items, segment_info, status);
+                   positions, segment_of_row, block_table, table_stride, page_size, *spec, items, segment_info, split_keys, max_splits,
+                   partial, status);
+    if (partial) {
+        if (act_bf16)
+            mlr_launch((attention_masked_merge_kernel<__nv_bfloat16>), dim3(merge_grid), dim3(kThreads), 0, stream, partial,
+                       static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(out), ldo, positions, *spec, items,
+                       segment_info, split_keys, max_splits);
+        else
+            mlr_launch((attention_masked_merge_kernel<float>), dim3(merge_grid), dim3(kThreads), 0, stream, partial,
+                       static_cast<const float*>(gate), ld_gate, static_cast<float*>(out), ldo, positions, *spec, items, segment_info,
+                       split_keys, max_splits);
+    }
     return mlr_launched("attention_masked");
 }
 

@@ -445,6 +445,160 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan_kernel(const 
         }
 }
 
+// The same walk for head sizes that are a multiple of 32, with a warp's lanes as 4 columns x 8 lanes: a lane keeps E4 groups of
+// four state values of ONE column (values 4 * (8 * e + lane % 8) + 0..3, so that the eight lanes of a column read 128
+// consecutive bytes of k and q at a time), and a sum over a column is 3 exchanges among 8 lanes instead of 5 among 32.
+template <typename T, int E4>
+__global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const float* qf, const float* kf, const float* gates, const T* proj,
+                                                                          int ld, float* obuf, float* state, long long state_stride,
+                                                                          const int* segment_info, RecurrenceSpec s, int batch) {
+    mlr_grid_dependents_may_start();
+    mlr_grid_wait();
+    extern __shared__ __align__(16) unsigned char smem[];
+    const size_t stage = static_cast<size_t>(batch) * s.dim;
+    float* qs = reinterpret_cast<float*>(smem);                // [2][batch][dim]: a batch is copied while the one before is walked
+    float* ks = qs + 2 * stage;                                // [2][batch][dim]
+    float* vs = ks + 2 * stage;                                // [batch][16]
+    float* os = vs + static_cast<size_t>(batch) * kScanBlockCols;   // [batch][16]
+    float* gs = os + static_cast<size_t>(batch) * kScanBlockCols;   // [batch]
+    float* bs = gs + batch;                                    // [batch]
+    const int segment = blockIdx.x, head = blockIdx.y, block_col = blockIdx.z * kScanBlockCols;
+    const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], slot = segment_info[4 * segment + 3];
+    const int qk_head = head / (s.heads / s.qk_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = block_col + warp * kScanCols;
+    const size_t qk_ld = static_cast<size_t>(s.qk_heads) * s.dim;
+    const size_t o_ld = static_cast<size_t>(s.heads) * s.vdim;
+    const bool wide = s.dim % 4 == 0;                          // rows of q and k start on 16-byte borders
+
+    const int sub = lane & 7, my_col = col0 + (lane >> 3);
+    const bool live = my_col < s.vdim;
+    float S[E4][4];
+    float* my_state = state + static_cast<size_t>(slot) * state_stride + (static_cast<size_t>(head) * s.vdim) * s.dim;
+#pragma unroll
+    for (int e = 0; e < E4; ++e)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) S[e][j] = live ? my_state[static_cast<size_t>(my_col) * s.dim + 4 * (8 * e + sub) + j] : 0.0f;
+    const float decay = s.rule == 0 ? s.decay[head] : 1.0f;
+
+    constexpr int kVPerThread = 32 * kScanBlockCols / (kScanWarps * 32);     // batch <= 32
+    float v_next[kVPerThread], g_next = 0.0f, b_next = 0.0f;
+    // Starts the copies of a batch's q and k into a stage and loads its v, g and beta into registers.
+    auto fetch = [&](int base, int into) {
+        const int n = min(batch, count - base);
+        const float* qsrc = qf + static_cast<size_t>(first + base) * qk_ld + static_cast<size_t>(qk_head) * s.dim;
+        const float* ksrc = kf + static_cast<size_t>(first + base) * qk_ld + static_cast<size_t>(qk_head) * s.dim;
+        float* qdst = qs + into * stage;
+        float* kdst = ks + into * stage;
+        if (wide) {
+            const int per_row = s.dim / 4;
+            for (int i = threadIdx.x; i < n * per_row; i += blockDim.x) {
+                const int t = i / per_row, c = (i % per_row) * 4;
+                mlr_async_copy16(qdst + static_cast<size_t>(t) * s.dim + c, qsrc + t * qk_ld + c);
+                mlr_async_copy16(kdst + static_cast<size_t>(t) * s.dim + c, ksrc + t * qk_ld + c);
+            }
+        } else {
+            for (int i = threadIdx.x; i < n * s.dim; i += blockDim.x) {
+                const int t = i / s.dim, c = i % s.dim;
+                mlr_async_copy4(qdst + static_cast<size_t>(t) * s.dim + c, qsrc + t * qk_ld + c);
+                mlr_async_copy4(kdst + static_cast<size_t>(t) * s.dim + c, ksrc + t * qk_ld + c);
+            }
+        }
+        mlr_async_commit();
+#pragma unroll
+        for (int j = 0; j < kVPerThread; ++j) {
+            const int i = threadIdx.x + j * kScanWarps * 32;
+            const int t = i / kScanBlockCols, c = block_col + i % kScanBlockCols;
+            v_next[j] = (t < n && c < s.vdim) ? mlr_load(proj + static_cast<size_t>(first + base + t) * ld, s.col_v + head * s.vdim + c) : 0.0f;
+        }
+        if (s.rule == 1 && threadIdx.x < n) {
+            g_next = __ldcg(gates + static_cast<size_t>(first + base + threadIdx.x) * 2 * s.heads + head);
+            b_next = __ldcg(gates + static_cast<size_t>(first + base + threadIdx.x) * 2 * s.heads + s.heads + head);
+        }
+    };
+
+    fetch(0, 0);
+    int current = 0;
+    for (int base = 0; base < count; base += batch, current ^= 1) {
+        const int n = min(batch, count - base);
+        __syncthreads();                    // the batch before has been walked and written out
+#pragma unroll
+        for (int j = 0; j < kVPerThread; ++j) {
+            const int i = threadIdx.x + j * kScanWarps * 32;
+            if (i < batch * kScanBlockCols) vs[i] = v_next[j];
+        }
+        if (threadIdx.x < batch) {
+            gs[threadIdx.x] = g_next;
+            bs[threadIdx.x] = b_next;
+        }
+        mlr_async_wait();
+        __syncthreads();
+        if (base + batch < count) fetch(base + batch, current ^ 1);
+        const float* qnow = qs + current * stage;
+        const float* know = ks + current * stage;
+        for (int t = 0; t < n; ++t) {
+            const float4* k4 = reinterpret_cast<const float4*>(know + static_cast<size_t>(t) * s.dim);
+            const float4* q4 = reinterpret_cast<const float4*>(qnow + static_cast<size_t>(t) * s.dim);
+            float4 kk[E4], qq[E4];
+#pragma unroll
+            for (int e = 0; e < E4; ++e) {
+                kk[e] = k4[8 * e + sub];
+                qq[e] = q4[8 * e + sub];
+            }
+            const float v = vs[t * kScanBlockCols + warp * kScanCols + (lane >> 3)];
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+            if (s.rule == 0) {
+#pragma unroll
+                for (int e = 0; e < E4; ++e) {
+                    S[e][0] = fmaf(decay, S[e][0], kk[e].x * v); d0 = fmaf(S[e][0], qq[e].x, d0);
+                    S[e][1] = fmaf(decay, S[e][1], kk[e].y * v); d1 = fmaf(S[e][1], qq[e].y, d1);
+                    S[e][2] = fmaf(decay, S[e][2], kk[e].z * v); d2 = fmaf(S[e][2], qq[e].z, d2);
+                    S[e][3] = fmaf(decay, S[e][3], kk[e].w * v); d3 = fmaf(S[e][3], qq[e].w, d3);
+                }
+            } else {
+                const float g = gs[t], beta = bs[t];
+                float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E4; ++e) {
+                    S[e][0] *= g; c0 = fmaf(S[e][0], kk[e].x, c0);
+                    S[e][1] *= g; c1 = fmaf(S[e][1], kk[e].y, c1);
+                    S[e][2] *= g; c2 = fmaf(S[e][2], kk[e].z, c2);
+                    S[e][3] *= g; c3 = fmaf(S[e][3], kk[e].w, c3);
+                }
+                float dk = (c0 + c1) + (c2 + c3);
+                dk += __shfl_xor_sync(0xffffffffu, dk, 1);
+                dk += __shfl_xor_sync(0xffffffffu, dk, 2);
+                dk += __shfl_xor_sync(0xffffffffu, dk, 4);
+                const float u = beta * (v - dk);
+#pragma unroll
+                for (int e = 0; e < E4; ++e) {
+                    S[e][0] = fmaf(kk[e].x, u, S[e][0]); d0 = fmaf(S[e][0], qq[e].x, d0);
+                    S[e][1] = fmaf(kk[e].y, u, S[e][1]); d1 = fmaf(S[e][1], qq[e].y, d1);
+                    S[e][2] = fmaf(kk[e].z, u, S[e][2]); d2 = fmaf(S[e][2], qq[e].z, d2);
+                    S[e][3] = fmaf(kk[e].w, u, S[e][3]); d3 = fmaf(S[e][3], qq[e].w, d3);
+                }
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if (sub == 0) os[t * kScanBlockCols + warp * kScanCols + (lane >> 3)] = dot;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * kScanBlockCols; i += blockDim.x) {
+            const int t = i / kScanBlockCols, c = block_col + i % kScanBlockCols;
+            if (c < s.vdim) obuf[static_cast<size_t>(first + base + t) * o_ld + static_cast<size_t>(head) * s.vdim + c] = os[i];
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int e = 0; e < E4; ++e)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) my_state[static_cast<size_t>(my_col) * s.dim + 4 * (8 * e + sub) + j] = S[e][j];
+    }
+}
+
+
 // Norm per head, weight, gate and the constant on the scan's float32 outputs [rows, heads * vdim].
 template <typename T>
 __global__ void __launch_bounds__(128) recurrence_readout_kernel(const float* obuf, const T* side, int ld_side, T* out, int ld_out,
@@ -583,7 +737,8 @@ static int check_recurrence(const RecurrenceSpec& s) {
 }
 
 // The three-kernel form.  qf, kf: float32 [rows, qk_heads * dim]; gates: float32 [rows, 2 * heads] (delta rule; else unused);
-// obuf: float32 [rows, heads * vdim].  Same results as `mlr_linear_recurrence` up to the order of no sum: both add in the same order.
+// obuf: float32 [rows, heads * vdim].  Same results as `mlr_linear_recurrence` up to the order in which a column's sums are added
+// (the same order for head sizes that are no multiple of 32).
 MLR_API int mlr_linear_recurrence_split(const RecurrenceSpec* spec, const void* proj, int ld, const void* side, int ld_side, int act_bf16,
                                         void* out, int ld_out, float* state, long long state_stride, const int* segment_info,
                                         int n_segments, const int* positions, int rows, float* qf, float* kf, float* gates, float* obuf,
@@ -600,11 +755,19 @@ MLR_API int mlr_linear_recurrence_split(const RecurrenceSpec* spec, const void* 
     batch = batch < 1 ? 1 : (batch > 32 ? 32 : batch);
     const size_t shared = per_token * batch;
     const dim3 grid(n_segments, s.heads, (s.vdim + kScanBlockCols - 1) / kScanBlockCols);
+#define MLR_SCAN8(T, E)                                                                                                                \
+    mlr_launch((recurrence_scan8_kernel<T, E>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates,                      \
+               static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch)
 #define MLR_SPLIT(T)                                                                                                                   \
     do {                                                                                                                               \
         mlr_launch((recurrence_prepare_kernel<T>), dim3(rows), dim3(128), 0, stream, static_cast<const T*>(proj), ld,                  \
                    static_cast<const T*>(side), ld_side, qf, kf, gates, positions, s);                                                 \
-        if (regs == 1) mlr_launch((recurrence_scan_kernel<T, 1>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates,    \
+        if (s.dim == 32) MLR_SCAN8(T, 1);                                                                                              \
+        else if (s.dim == 64) MLR_SCAN8(T, 2);                                                                                         \
+        else if (s.dim == 96) MLR_SCAN8(T, 3);                                                                                         \
+        else if (s.dim == 128) MLR_SCAN8(T, 4);                                                                                        \
+        else if (s.dim == 256) MLR_SCAN8(T, 8);                                                                                        \
+        else if (regs == 1) mlr_launch((recurrence_scan_kernel<T, 1>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates,    \
                                   static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch);                 \
         else if (regs == 2) mlr_launch((recurrence_scan_kernel<T, 2>), dim3(grid), dim3(kScanWarps * 32), shared, stream, qf, kf, gates, \
                                        static_cast<const T*>(proj), ld, obuf, state, state_stride, segment_info, s, batch);            \
@@ -618,6 +781,7 @@ MLR_API int mlr_linear_recurrence_split(const RecurrenceSpec* spec, const void* 
     if (act_bf16) MLR_SPLIT(__nv_bfloat16);
     else MLR_SPLIT(float);
 #undef MLR_SPLIT
+#undef MLR_SCAN8
     return mlr_launched("linear_recurrence_split");
 }
 

@@ -95,19 +95,23 @@ class MaskedAttentionMixer(SequenceCore):
         args = (address(self.desc), proj.ptr, proj.ld, gate.ptr if gate else None, gate.ld if gate else 0, act.ptr, act.ld)
         where = (run.cache.data_ptr(), run.cache.shape[0])
         tiled = (proj.dtype is torch.bfloat16 and native.module("attention_masked").mlr_attention_masked_tiles_fit(self.dim, self.vdim)
-                 and act.ld % 2 == 0)
+                 and act.ld % 2 == 0 and act.ptr % 4 == 0)
         if not tiled:
             # One block per (row, head): the float32 path, and sizes the tiled kernel does not take.
             b.launch("attention_masked", "mlr_attention_masked", *args, proj.is_bf16, *where, b.meta("positions"),
-                     b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, b.status, b.stream)
+                     b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, 0, 1, None, b.status, b.stream)
             return
         # The step's launch plan (made by the native executor from the step's segments, shared by all layers):
         # segments of few rows (a decoded token, a short portion) go to the row kernel, prompt portions in tiles of 64
         # rows to the tensor-core kernel.
-        plan = b.plan((self.heads // self.kv_heads if self.heads // self.kv_heads <= 16 else 1, self.kv_heads, 0, 0, self.dim, 1))
+        # The row kernel cuts long contexts into key ranges that run as blocks of their own (the plan's split of the keys and
+        # its scratch for the ranges' partial results: 16 rows x kv heads x splits x (head size + 2) floats per segment).
+        group = self.heads // self.kv_heads
+        plan = b.plan((group if group <= 16 else 1, self.kv_heads, 0, 0, max(self.dim, self.vdim), 1))
         info = b.meta("segment_info")
+        split = (plan.chunk, plan.max_splits, plan.scratch) if group <= 16 else (0, 1, None)
         b.launch("attention_masked", "mlr_attention_masked", *args, 1, *where, b.meta("positions"), b.meta("segment_of_row"), table,
-                 stride, b.page_size, 0, plan.items, plan.n_items, info, b.status, b.stream, need=plan.n_items)
+                 stride, b.page_size, 0, plan.items, plan.n_items, info, *split, b.status, b.stream, need=plan.n_items)
         b.launch("attention_masked", "mlr_attention_masked_tiles", *args, *where, plan.tiles, plan.n_tiles, info, table, stride,
                  b.page_size, b.status, b.stream, need=plan.n_tiles)
 

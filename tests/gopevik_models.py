@@ -55,7 +55,23 @@ SMALL_C = {
     "layers": [_delta(2, 2, 16, 16, 4, None), _delta(4, 2, 8, 8, 3, 48)],
 }
 
-ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "small_c": SMALL_C}
+# Sizes that miss every fast path: a width that is no multiple of 8, head sizes that are no multiple of 16 or 8,
+# an odd number of rotated pairs, a chunk of one page and a bit, equal scales, one head everywhere.
+SMALL_D = {
+    "architecture": "Gopevik", "vocab": 77, "width": 36, "norm": {"eps": 1e-5, "groups": 2},
+    "layers": [
+        _parallel({"heads": 1, "kv_heads": 1, "dim": 12, "vdim": 20, "scale": 0.4, "mask": {"size": 9},
+                   "rot": {"base": 30.0, "dims": 6, "scaling": {"factor": 1.5}}},
+                  {"heads": 1, "dim": 10, "vdim": 6, "decay": [0.93], "rot": {"base": 400.0, "dims": 10}},
+                  1.0, 1.0, 50),
+        _delta(1, 1, 24, 12, 4, 22),
+        _parallel({"heads": 3, "kv_heads": 1, "dim": 16, "vdim": 24, "scale": 0.2, "mask": {"size": 1000}},
+                  {"heads": 2, "dim": 34, "vdim": 18, "decay": [0.5, 1.0]},
+                  0.5, 2.0, None),
+    ],
+}
+
+ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "small_c": SMALL_C, "small_d": SMALL_D}
 
 
 def get(name: str) -> dict:

@@ -161,7 +161,7 @@ def test_gated_bias_kernel(activation):
     assert torch.allclose(out.cpu().double(), act * up, atol=1e-5, rtol=1e-5)
 
 
-def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, window, sink, gate, T, page, boost=None, seed=0, tiled=0):
+def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, window, sink, gate, T, page, boost=None, seed=0, tiled=0, split=None):
     """One request of T tokens written into a paged cache with shuffled pages, then every row's attention."""
     from mini_llm_runtime_b200.ops import native
     from mini_llm_runtime_b200.ops.specs import GATES, MaskedAttentionSpec
@@ -203,9 +203,16 @@ def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, 
         two = torch.cat([table, table]).contiguous()
         _call("attention_masked", "mlr_attention_masked_tiles", *common, cache.data_ptr(), n_pages, tiles.data_ptr(), tiles.shape[0],
               info.data_ptr(), two.data_ptr(), two.stride(0), page, status.data_ptr(), native.stream())
+    elif split:     # the last rows as a segment of few rows, its keys cut into ranges that are added up afterwards
+        last, keys, most = split
+        info = torch.tensor([[T - last, last, T - last, 0]], dtype=torch.int32, device=dev)
+        partial = torch.full((16 * kv_heads * most * (vdim + 2),), float("nan"), device=dev)
+        _call("attention_masked", "mlr_attention_masked", *common, is16, cache.data_ptr(), n_pages, positions.data_ptr(),
+              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, 0, None, 1, info.data_ptr(), keys, most, partial.data_ptr(),
+              status.data_ptr(), native.stream())
     else:
         _call("attention_masked", "mlr_attention_masked", *common, is16, cache.data_ptr(), n_pages, positions.data_ptr(),
-              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, None, 0, None, status.data_ptr(), native.stream())
+              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, None, 0, None, 0, 1, None, status.data_ptr(), native.stream())
     assert int(status.item()) == 0
     pos = torch.arange(T)
     qd = plain.rotate_half(q.double().cpu().view(T, heads, dim), pos, rot_dims, base, factor) if rot_dims else q.double().cpu().view(T, heads, dim)
@@ -233,6 +240,8 @@ def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, 
     if gate:
         gd = gates.double().cpu()
         want = want * (torch.sigmoid(gd) if gate == "sigmoid" else plain.silu(gd))
+    if split:
+        return out[T - split[0]:].float().cpu().double(), want[T - split[0]:] * 0.75
     return out.float().cpu().double(), want * 0.75
 
 
@@ -264,6 +273,20 @@ def test_masked_attention_in_tiles_on_the_tensor_cores(case):
     """Prompt portions in bfloat16: tiles of 64 rows of two portions of one request, the second continuing the first."""
     got, want = _attention_case(torch.bfloat16, **case)
     assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), float((got - want).abs().max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", [
+    dict(heads=4, kv_heads=2, dim=24, vdim=16, rot_dims=8, factor=1.0, chunk=None, window=None, sink=True, gate="sigmoid", T=700, page=16, split=(5, 128, 6)),
+    dict(heads=2, kv_heads=2, dim=16, vdim=40, rot_dims=16, factor=2.0, chunk=300, window=None, sink=True, gate=None, T=650, page=8, split=(8, 64, 11)),
+    dict(heads=3, kv_heads=1, dim=8, vdim=8, rot_dims=0, factor=1.0, chunk=None, window=None, sink=False, gate="silu", T=333, page=16, split=(1, 192, 2)),
+    dict(heads=1, kv_heads=1, dim=32, vdim=200, rot_dims=4, factor=1.0, chunk=100, window=None, sink=True, gate=None, T=402, page=16, split=(16, 64, 7)),
+])
+def test_masked_attention_with_the_keys_cut_into_ranges(dtype, case):
+    got, want = _attention_case(dtype, **case)
+    tol = 2e-5 if dtype is torch.float32 else 3e-2
+    assert torch.allclose(got, want, atol=tol, rtol=tol), float((got - want).abs().max())
 
 
 @pytest.mark.gpu
@@ -376,6 +399,10 @@ def _recurrence_case(dtype, rule, heads, qk_heads, dim, vdim, rot_dims, segments
     dict(rule="delta", heads=4, qk_heads=2, dim=16, vdim=8, rot_dims=0, segments=[50, 3, 1, 18]),
     dict(rule="delta", heads=2, qk_heads=2, dim=64, vdim=200, rot_dims=0, segments=[40]),
     dict(rule="delta", heads=6, qk_heads=1, dim=8, vdim=33, rot_dims=0, segments=[2, 65]),
+    dict(rule="delta", heads=2, qk_heads=1, dim=96, vdim=20, rot_dims=0, segments=[70, 9]),
+    dict(rule="decay", heads=2, qk_heads=2, dim=128, vdim=128, rot_dims=64, segments=[100]),
+    dict(rule="decay", heads=1, qk_heads=1, dim=32, vdim=7, rot_dims=32, segments=[3, 40]),
+    dict(rule="delta", heads=1, qk_heads=1, dim=256, vdim=17, rot_dims=0, segments=[35]),
 ])
 @pytest.mark.parametrize("split", [False, True])
 def test_recurrence_kernel_with_state_carried_between_steps(dtype, case, split):
@@ -383,7 +410,7 @@ def test_recurrence_kernel_with_state_carried_between_steps(dtype, case, split):
     tol = 3e-5 if dtype is torch.float32 else 4e-2
     for i, (a, b) in enumerate(zip(got, want)):
         assert torch.allclose(a, b, atol=tol, rtol=tol), (i, float((a - b).abs().max()))
-    if split:       # prepare / scan / read-out add in the order of the one kernel: the same bits
+    if split and case["dim"] % 32:       # prepare / scan / read-out add in the order of the one kernel: the same bits
         fused, _ = _recurrence_case(dtype, split=False, **case)
         for a, b in zip(got, fused):
             assert torch.equal(a, b)
