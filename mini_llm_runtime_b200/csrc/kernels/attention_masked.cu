@@ -40,7 +40,6 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
                                                                  const int* positions, const int* segment_of_row,
                                                                  const int* block_table, int table_stride, int page_size,
                                                                  MaskedAttentionSpec s, int* status) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const int row = blockIdx.x;
     const int position = positions[row];
@@ -72,6 +71,7 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
         const int head = i / s.vdim, c = i % s.vdim;
         vbase[static_cast<size_t>(head) * page_size * s.vdim + c] = vrow[i];
     }
+    mlr_grid_dependents_may_start();
 }
 
 template <typename T>
@@ -81,7 +81,6 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
                                                                     int table_stride, int page_size, MaskedAttentionSpec s,
                                                                     const int* items, const int* segment_info, int split_keys,
                                                                     int max_splits, float* partial, int* status) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     long long* offsets = reinterpret_cast<long long*>(smem);   // [kTile] element offset of the token's value row
@@ -204,22 +203,30 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
             running_sum *= alpha;
 #pragma unroll
             for (int d = 0; d < kMaxDimsPerThread; ++d) acc[d] *= alpha;
-            for (int i = 0; i < kTile; ++i) {
-                const long long offset = offsets[i];
-                if (offset < 0) continue;
-                const float w = scores[i];
-                running_sum += w;
-                const T* v = cache + offset;
+            for (int i0 = 0; i0 < kTile; i0 += 8) {       // eight keys' values are on their way before the first is used
+                float values[8][kMaxDimsPerThread];
 #pragma unroll
-                for (int d = 0; d < kMaxDimsPerThread; ++d) {
-                    const int c = threadIdx.x + d * kThreads;
-                    if (c < s.vdim) acc[d] = fmaf(w, mlr_load(v, c), acc[d]);
+                for (int u = 0; u < 8; ++u) {
+                    const long long offset = offsets[i0 + u];
+#pragma unroll
+                    for (int d = 0; d < kMaxDimsPerThread; ++d) {
+                        const int c = threadIdx.x + d * kThreads;
+                        values[u][d] = (offset >= 0 && c < s.vdim) ? mlr_load(cache + offset, c) : 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float w = scores[i0 + u];         // 0 for a key that is not seen
+                    running_sum += w;
+#pragma unroll
+                    for (int d = 0; d < kMaxDimsPerThread; ++d) acc[d] = fmaf(w, values[u][d], acc[d]);
                 }
             }
             running_max = new_max;
         }
         __syncthreads();
     }
+    mlr_grid_dependents_may_start();
     if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
     if (partial) {
         const int j = blockIdx.x % kRowsPerItem;
@@ -258,7 +265,6 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const float* partial, const T* gate, int ld_gate, T* out, int ldo,
                                                                           const int* positions, MaskedAttentionSpec s, const int* items,
                                                                           const int* segment_info, int split_keys, int max_splits) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const int item = blockIdx.x / kRowsPerItem, j = blockIdx.x % kRowsPerItem, head = blockIdx.y;
     const int* info = segment_info + 4 * (items ? items[item] : item);
@@ -301,6 +307,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
             mlr_store(orow, c, value * s.out_scale);
         }
     }
+    mlr_grid_dependents_may_start();
 }
 
 // ---- prompt portions in bfloat16: 64 query rows of one request and one head per block, on the tensor cores.
@@ -333,7 +340,6 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                                                                     __nv_bfloat16* out, int ldo, const __nv_bfloat16* cache, int num_pages,
                                                                     const int* tiles, const int* segment_info, const int* block_table,
                                                                     int table_stride, int page_size, MaskedAttentionSpec s, int* status) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     const int qstride = s.dim + kPad, vstride = s.vdim + kPad;
@@ -495,6 +501,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
             }
         }
     }
+    mlr_grid_dependents_may_start();     // only now: blocks of the next grid that wait on this SM would take its room
     if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);

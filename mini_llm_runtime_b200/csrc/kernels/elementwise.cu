@@ -441,7 +441,6 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 template <typename T>
 __global__ void gated_bias_kernel(const T* gate_up, int ld, const float* bias_gate, const float* bias_up, T* out, int ld_out,
                                   int rows, int inter, int activation) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const size_t total = static_cast<size_t>(rows) * inter;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -453,6 +452,7 @@ __global__ void gated_bias_kernel(const T* gate_up, int ld, const float* bias_ga
                                         : g / (1.0f + expf(-g));
         mlr_store(out, r * ld_out + c, a * u);
     }
+    mlr_grid_dependents_may_start();
 }
 
 template <typename T>

@@ -32,7 +32,6 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const float* delta, int ld_delta, const float* bias,
                                                                  const float* w_post, const float* w_pre, T* out, int ld_out,
                                                                  const int* rows, int width, int groups, float eps, int norm_delta) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     float* vals = reinterpret_cast<float*>(smem);
@@ -64,6 +63,7 @@ __global__ void __launch_bounds__(kThreads) group_rmsnorm_kernel(float* h, const
         const float normed = vals[i] * inv[i / part];
         mlr_store(o, i, w_pre ? normed * w_pre[i] : normed);
     }
+    mlr_grid_dependents_may_start();
 }
 
 }  // namespace

@@ -50,7 +50,6 @@ template <typename T, int R, int COLS>
 __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, int ld, const T* side, int ld_side, T* out, int ld_out, float* state,
                                                                   long long state_stride, const int* segment_info, RecurrenceSpec s,
                                                                   int batch) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     float* qs = reinterpret_cast<float*>(smem);          // [batch][dim]
@@ -220,6 +219,7 @@ __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, 
         }
         __syncthreads();
     }
+    mlr_grid_dependents_may_start();
 #pragma unroll
     for (int c = 0; c < COLS; ++c)
 #pragma unroll
@@ -238,7 +238,6 @@ __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, 
 template <typename T>
 __global__ void __launch_bounds__(128) recurrence_prepare_kernel(const T* proj, int ld, const T* side, int ld_side, float* qf, float* kf,
                                                                  float* gates, const int* positions, RecurrenceSpec s) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -281,6 +280,7 @@ __global__ void __launch_bounds__(128) recurrence_prepare_kernel(const T* proj, 
             gates[static_cast<size_t>(row) * 2 * s.heads + s.heads + h] = 1.0f / (1.0f + expf(-b));
         }
     }
+    mlr_grid_dependents_may_start();
 }
 
 constexpr int kScanWarps = 4, kScanCols = 4, kScanBlockCols = kScanWarps * kScanCols;
@@ -289,7 +289,6 @@ template <typename T, int R>
 __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan_kernel(const float* qf, const float* kf, const float* gates, const T* proj,
                                                                           int ld, float* obuf, float* state, long long state_stride,
                                                                           const int* segment_info, RecurrenceSpec s, int batch) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     const size_t stage = static_cast<size_t>(batch) * s.dim;
@@ -436,6 +435,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan_kernel(const 
             if (c < s.vdim) obuf[static_cast<size_t>(first + base + t) * o_ld + static_cast<size_t>(head) * s.vdim + c] = os[i];
         }
     }
+    mlr_grid_dependents_may_start();     // only now: blocks of the next grid that wait on this SM slow the walk
 #pragma unroll
     for (int c = 0; c < kScanCols; ++c)
 #pragma unroll
@@ -452,7 +452,6 @@ template <typename T, int E4>
 __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const float* qf, const float* kf, const float* gates, const T* proj,
                                                                           int ld, float* obuf, float* state, long long state_stride,
                                                                           const int* segment_info, RecurrenceSpec s, int batch) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     const size_t stage = static_cast<size_t>(batch) * s.dim;
@@ -590,6 +589,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
             if (c < s.vdim) obuf[static_cast<size_t>(first + base + t) * o_ld + static_cast<size_t>(head) * s.vdim + c] = os[i];
         }
     }
+    mlr_grid_dependents_may_start();     // only now: blocks of the next grid that wait on this SM slow the walk
     if (live) {
 #pragma unroll
         for (int e = 0; e < E4; ++e)
@@ -603,7 +603,6 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
 template <typename T>
 __global__ void __launch_bounds__(128) recurrence_readout_kernel(const float* obuf, const T* side, int ld_side, T* out, int ld_out,
                                                                  RecurrenceSpec s) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -631,13 +630,13 @@ __global__ void __launch_bounds__(128) recurrence_readout_kernel(const float* ob
             mlr_store(orow, c, value * s.out_scale);
         }
     }
+    mlr_grid_dependents_may_start();
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) short_conv_kernel(const T* in, int ld_in, T* out, int ld_out, int channels, int taps,
                                                          const float* weights, const float* state, long long state_stride,
                                                          const int* segment_info, const int* segment_of_row) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const int row = blockIdx.x;
     const int segment = segment_of_row[row];
@@ -654,6 +653,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const T* in, int ld_in,
         }
         mlr_store(out + static_cast<size_t>(row) * ld_out, c, y / (1.0f + expf(-y)));
     }
+    mlr_grid_dependents_may_start();
 }
 
 constexpr int kMaxTaps = 16;
@@ -661,7 +661,6 @@ constexpr int kMaxTaps = 16;
 template <typename T>
 __global__ void __launch_bounds__(256) short_conv_state_kernel(const T* in, int ld_in, int channels, int taps, float* state,
                                                                long long state_stride, const int* segment_info) {
-    mlr_grid_dependents_may_start();
     mlr_grid_wait();
     const int segment = blockIdx.x;
     const int first = segment_info[4 * segment], count = segment_info[4 * segment + 1], slot = segment_info[4 * segment + 3];
@@ -675,6 +674,7 @@ __global__ void __launch_bounds__(256) short_conv_state_kernel(const T* in, int 
                 m >= 0 ? mlr_load(in + static_cast<size_t>(first + m) * ld_in, c) : kept[taps - 1 + m];
         }
     }
+    mlr_grid_dependents_may_start();
 }
 
 }  // namespace
