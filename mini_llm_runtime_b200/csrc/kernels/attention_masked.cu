@@ -323,6 +323,17 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -389,6 +400,8 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     for (int nv = 0; nv < NV; ++nv) O[nv][0] = O[nv][1] = O[nv][2] = O[nv][3] = 0.0f;
     const int ksteps = s.dim / 16;
     const uint32_t vs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Vs));
+    const uint32_t qs_base = static_cast<uint32_t>(__cvta_generic_to_shared(Qs));
+    const uint32_t ks_base = static_cast<uint32_t>(__cvta_generic_to_shared(Ks));
 
     // Keys and values of a tile of 64 positions go from their pages into one of two stages by asynchronous copies, so
     // that the next tile arrives while this one is multiplied; rows no query of the block may see become zeros.
@@ -423,22 +436,32 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
         mlr_async_wait();
         __syncthreads();      // this tile has arrived (and Qs is written); no warp still reads the other stage
         if (kt + kKeys <= last_pos) fetch(kt + kKeys, current ^ 1);
-        const __nv_bfloat16* Kt = Ks + current * kKeys * qstride;
+        const uint32_t kt_base = ks_base + static_cast<uint32_t>(current * kKeys * qstride * 2);
         const uint32_t vt_base = vs_base + static_cast<uint32_t>(current * kKeys * vstride * 2);
         float S[8][4];
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.0f;
-        for (int ks = 0; ks < ksteps; ++ks) {
-            uint32_t a[4];
-            const __nv_bfloat16* qa = Qs + (r0 + g) * qstride + ks * 16 + 2 * t;
-            a[0] = *reinterpret_cast<const uint32_t*>(qa);
-            a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * qstride);
-            a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
-            a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * qstride + 8);
+        // Fragments by ldmatrix: one x4 gives the 16 x 16 piece of Q; one x4 gives, for 8 keys, the pieces of two
+        // steps of 16 along the head (a last odd step takes an x2).
+        const uint32_t q_row = qs_base + static_cast<uint32_t>(((r0 + (lane & 7) + ((lane >> 3) & 1) * 8) * qstride + (lane >> 4) * 8) * 2);
+        const uint32_t k_row = kt_base + static_cast<uint32_t>((((lane & 7)) * qstride + (lane >> 3) * 8) * 2);
+        for (int ks = 0; ks < ksteps; ks += 2) {
+            uint32_t a[4], a2[4] = {0, 0, 0, 0};
+            ldmatrix_x4(a, q_row + ks * 32);
+            const bool two = ks + 1 < ksteps;
+            if (two) ldmatrix_x4(a2, q_row + (ks + 1) * 32);
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
-                const __nv_bfloat16* kb = Kt + (nt * 8 + g) * qstride + ks * 16 + 2 * t;
-                mma_bf16(S[nt], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+                uint32_t kb[4];
+                const uint32_t at = k_row + static_cast<uint32_t>((nt * 8 * qstride + ks * 16) * 2);
+                if (two) {
+                    ldmatrix_x4(kb, at);
+                    mma_bf16(S[nt], a, kb[0], kb[1]);
+                    mma_bf16(S[nt], a2, kb[2], kb[3]);
+                } else {
+                    ldmatrix_x2(kb, at);
+                    mma_bf16(S[nt], a, kb[0], kb[1]);
+                }
             }
         }
         // mask, running maximum
@@ -459,8 +482,8 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
         tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 1));
         tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 2));
         const float new_a = fmaxf(m_a, tile_a), new_b = fmaxf(m_b, tile_b);
-        const float alpha_a = (m_a == -INFINITY) ? 0.0f : expf(m_a - new_a);
-        const float alpha_b = (m_b == -INFINITY) ? 0.0f : expf(m_b - new_b);
+        const float alpha_a = (m_a == -INFINITY) ? 0.0f : __expf(m_a - new_a);
+        const float alpha_b = (m_b == -INFINITY) ? 0.0f : __expf(m_b - new_b);
         m_a = new_a;
         m_b = new_b;
         l_a *= alpha_a;
@@ -474,7 +497,7 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float m = e < 2 ? new_a : new_b;
-                const float p = S[nt][e] == -INFINITY ? 0.0f : expf(S[nt][e] - m);
+                const float p = S[nt][e] == -INFINITY ? 0.0f : __expf(S[nt][e] - m);     // ex2.approx: 2 ulp, weights stay float32
                 S[nt][e] = p;
                 if (e < 2) l_a += p; else l_b += p;
             }
@@ -489,14 +512,16 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                 hi[j] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
                 lo[j] = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
             }
-            const uint32_t row_addr = vt_base + static_cast<uint32_t>(((kk * 16 + (lane & 15)) * vstride) * 2);
+            const uint32_t row_addr = vt_base + static_cast<uint32_t>(((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * vstride + (lane >> 4) * 8) * 2);
 #pragma unroll
-            for (int nv = 0; nv < NV; ++nv) {
-                if (nv * 8 < s.vdim) {
-                    uint32_t b0, b1;
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(row_addr + nv * 16));
-                    mma_bf16(O[nv], hi, b0, b1);
-                    mma_bf16(O[nv], lo, b0, b1);
+            for (int nv = 0; nv < NV; nv += 2) {
+                if (nv * 8 < s.vdim) {          // the second tile of a pair may lie in the row's padding: it is computed and never stored
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, row_addr + nv * 16);
+                    mma_bf16(O[nv], hi, vb[0], vb[1]);
+                    mma_bf16(O[nv], lo, vb[0], vb[1]);
+                    mma_bf16(O[nv + 1], hi, vb[2], vb[3]);
+                    mma_bf16(O[nv + 1], lo, vb[2], vb[3]);
                 }
             }
         }

@@ -535,6 +535,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
         if (base + batch < count) fetch(base + batch, current ^ 1);
         const float* qnow = qs + current * stage;
         const float* know = ks + current * stage;
+#pragma unroll 4
         for (int t = 0; t < n; ++t) {
             const float4* k4 = reinterpret_cast<const float4*>(know + static_cast<size_t>(t) * s.dim);
             const float4* q4 = reinterpret_cast<const float4*>(qnow + static_cast<size_t>(t) * s.dim);

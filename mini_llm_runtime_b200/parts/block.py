@@ -64,12 +64,20 @@ class SandwichBlock(Block):
         b.norm_ahead = None
         x = self.norms["pre_mixer"].emit(b, h, pending)
         mixed = self.mixer.emit(b, x, run)
+        # The norm behind the block's last sub-layer also applies the first norm of the block that follows (the model
+        # names it in `norm_after_block`), whose `emit` then finds the result in `prepared` and launches nothing.
+        after = b.norm_after_block
+        following = after[1] if after is not None and after[0] == "group_rms" else None
+        last = "post_mixer" if self.feed_forward is None else "post_feed_forward"
+        if following is not None and not self.norms[last].same_shape(following):
+            following = None
         if self.feed_forward is None:
-            self.norms["post_mixer"].emit_residual(b, h, mixed)
-            return None
-        x = self.norms["post_mixer"].emit_residual(b, h, mixed, then=self.norms["pre_feed_forward"])
-        out = self.feed_forward.emit(b, x)
-        self.norms["post_feed_forward"].emit_residual(b, h, out)
+            ahead = self.norms["post_mixer"].emit_residual(b, h, mixed, then=following)
+        else:
+            x = self.norms["post_mixer"].emit_residual(b, h, mixed, then=self.norms["pre_feed_forward"])
+            out = self.feed_forward.emit(b, x)
+            ahead = self.norms["post_feed_forward"].emit_residual(b, h, out, then=following)
+        b.prepared = {"group_rms": following, "stream": h, "out": ahead} if following is not None else None
         return None
 
 

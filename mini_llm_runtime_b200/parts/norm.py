@@ -90,9 +90,18 @@ class GroupRmsNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.weight = rt.vector(tensors[self.spec.weights["weight"]]).float()
 
+    def foldable(self):
+        """The block before may apply this norm in the launch that ends it (`emit_residual(then=...)`) and leave the
+        result on the builder (`prepared`)."""
+        return ("group_rms", self)
+
     def emit(self, b, h, delta, wanted_only: bool = False):
         if delta is not None and (delta.slices or wanted_only):
             raise native.KernelError("the grouped norm adds a plain [rows, width] contribution for all rows only")
+        prepared, b.prepared = b.prepared, None
+        if (delta is None and not wanted_only and isinstance(prepared, dict) and prepared.get("group_rms") is self
+                and prepared.get("stream") is h):
+            return prepared["out"]          # the launch that ended the block before has applied this norm already
         count = b.want if wanted_only else h.rows
         out = b.temp(count, self.width, b.rt.dtype)
         bias = getattr(delta, "bias", None) if delta is not None else None
@@ -102,11 +111,14 @@ class GroupRmsNorm(Norm):
                  self.width, self.groups, self.eps, 0, b.stream, need="want" if wanted_only else None)
         return out
 
+    def same_shape(self, other) -> bool:
+        return isinstance(other, GroupRmsNorm) and (other.width, other.groups, other.eps) == (self.width, self.groups, self.eps)
+
     def emit_residual(self, b, h, delta, then: Optional["GroupRmsNorm"] = None):
         """h += norm(delta + its bias) * weight; returns then(h) in the activation dtype, or None."""
         if delta.slices:
             raise native.KernelError("the grouped norm takes a plain [rows, width] contribution")
-        if then is not None and (then.width, then.groups, then.eps) != (self.width, self.groups, self.eps):
+        if then is not None and not self.same_shape(then):
             out = None
         else:
             out = b.temp(h.rows, self.width, b.rt.dtype) if then is not None else None
