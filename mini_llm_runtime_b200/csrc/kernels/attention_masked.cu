@@ -405,28 +405,30 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
 
     // Keys and values of a tile of 64 positions go from their pages into one of two stages by asynchronous copies, so
     // that the next tile arrives while this one is multiplied; rows no query of the block may see become zeros.
-    const int kchunks = s.dim / 8, vchunks = s.vdim / 8;
     auto fetch = [&](int kt, int into) {
         __nv_bfloat16* kdst = Ks + into * kKeys * qstride;
         __nv_bfloat16* vdst = Vs + into * kKeys * vstride;
-        for (int i = threadIdx.x; i < kKeys * (kchunks + vchunks); i += 128) {
-            const int key = i / (kchunks + vchunks), c = i % (kchunks + vchunks);
-            const int position = kt + key;
-            const __nv_bfloat16* src = cache;
-            bool real = position >= lo_min && position <= last_pos;
-            if (real) {
-                const int page = table[position / page_size];
-                if (page < 0 || page >= num_pages) {
-                    bad = 1;
-                    real = false;
-                } else {
-                    const size_t in_page = static_cast<size_t>(kv_head) * page_size + position % page_size;
-                    src = c < kchunks ? cache + page * page_elems + in_page * s.dim + c * 8
-                                      : cache + page * page_elems + key_plane + in_page * s.vdim + (c - kchunks) * 8;
-                }
+        // Two threads per key: the page and the row's addresses once, then every other 16-byte piece of the key's row
+        // and of its value row.
+        const int key = threadIdx.x >> 1, position = kt + key;
+        bool real = position >= lo_min && position <= last_pos;
+        const __nv_bfloat16* ksrc = cache;
+        const __nv_bfloat16* vsrc = cache;
+        if (real) {
+            const int page = table[position / page_size];
+            if (page < 0 || page >= num_pages) {
+                bad = 1;
+                real = false;
+            } else {
+                const size_t in_page = static_cast<size_t>(kv_head) * page_size + position % page_size;
+                ksrc = cache + page * page_elems + in_page * s.dim;
+                vsrc = cache + page * page_elems + key_plane + in_page * s.vdim;
             }
-            mlr_async_copy16(c < kchunks ? kdst + key * qstride + c * 8 : vdst + key * vstride + (c - kchunks) * 8, src, real);
         }
+        __nv_bfloat16* krow = kdst + key * qstride;
+        __nv_bfloat16* vrow = vdst + key * vstride;
+        for (int c = (threadIdx.x & 1) * 8; c < s.dim; c += 16) mlr_async_copy16(krow + c, real ? ksrc + c : cache, real);
+        for (int c = (threadIdx.x & 1) * 8; c < s.vdim; c += 16) mlr_async_copy16(vrow + c, real ? vsrc + c : cache, real);
         mlr_async_commit();
     };
     const int kt_first = (lo_min / kKeys) * kKeys;
@@ -464,19 +466,32 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
                 }
             }
         }
-        // mask, running maximum
+        // mask, running maximum.  A tile whose 64 keys every one of the warp's 16 rows sees needs no mask (the same for
+        // all lanes of a warp): all rows exist, the last key is at or before the first row, the first key at or after
+        // the last row's first visible one.
         float tile_a = -INFINITY, tile_b = -INFINITY;
+        const int warp_first = first_pos + r0, warp_last = warp_first + 15;
+        const bool open = r0 + 15 < n_rows && kt + kKeys - 1 <= warp_first && kt >= first_visible(warp_last, s);
+        if (open) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = kt + nt * 8 + 2 * t + (e & 1);
-                const bool upper = e < 2;
-                const bool seen = upper ? (row_a && key <= pos_a && key >= lo_a) : (row_b && key <= pos_b && key >= lo_b);
-                const float v = seen ? S[nt][e] * s.scale : -INFINITY;
-                S[nt][e] = v;
-                if (upper) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
+            for (int nt = 0; nt < 8; ++nt) {
+                S[nt][0] *= s.scale; S[nt][1] *= s.scale; S[nt][2] *= s.scale; S[nt][3] *= s.scale;
+                tile_a = fmaxf(tile_a, fmaxf(S[nt][0], S[nt][1]));
+                tile_b = fmaxf(tile_b, fmaxf(S[nt][2], S[nt][3]));
             }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = kt + nt * 8 + 2 * t + (e & 1);
+                    const bool upper = e < 2;
+                    const bool seen = upper ? (row_a && key <= pos_a && key >= lo_a) : (row_b && key <= pos_b && key >= lo_b);
+                    const float v = seen ? S[nt][e] * s.scale : -INFINITY;
+                    S[nt][e] = v;
+                    if (upper) tile_a = fmaxf(tile_a, v); else tile_b = fmaxf(tile_b, v);
+                }
+        }
         tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 1));
         tile_a = fmaxf(tile_a, __shfl_xor_sync(0xffffffffu, tile_a, 2));
         tile_b = fmaxf(tile_b, __shfl_xor_sync(0xffffffffu, tile_b, 1));

@@ -535,54 +535,70 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
         if (base + batch < count) fetch(base + batch, current ^ 1);
         const float* qnow = qs + current * stage;
         const float* know = ks + current * stage;
-#pragma unroll 4
-        for (int t = 0; t < n; ++t) {
-            const float4* k4 = reinterpret_cast<const float4*>(know + static_cast<size_t>(t) * s.dim);
-            const float4* q4 = reinterpret_cast<const float4*>(qnow + static_cast<size_t>(t) * s.dim);
-            float4 kk[E4], qq[E4];
+        // Four tokens at a time: their sums over a column are exchanged together, and nothing is stored to shared
+        // memory in between (a store there would keep the next token's loads from starting early).
+        for (int t0 = 0; t0 < n; t0 += 4) {
+            float dots[4];
 #pragma unroll
-            for (int e = 0; e < E4; ++e) {
-                kk[e] = k4[8 * e + sub];
-                qq[e] = q4[8 * e + sub];
+            for (int u = 0; u < 4; ++u) {
+                const int t = t0 + u;
+                dots[u] = 0.0f;
+                if (t < n) {
+                    const float4* k4 = reinterpret_cast<const float4*>(know + static_cast<size_t>(t) * s.dim);
+                    const float4* q4 = reinterpret_cast<const float4*>(qnow + static_cast<size_t>(t) * s.dim);
+                    float4 kk[E4], qq[E4];
+#pragma unroll
+                    for (int e = 0; e < E4; ++e) {
+                        kk[e] = k4[8 * e + sub];
+                        qq[e] = q4[8 * e + sub];
+                    }
+                    const float v = vs[t * kScanBlockCols + warp * kScanCols + (lane >> 3)];
+                    float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+                    if (s.rule == 0) {
+#pragma unroll
+                        for (int e = 0; e < E4; ++e) {
+                            S[e][0] = fmaf(decay, S[e][0], kk[e].x * v); d0 = fmaf(S[e][0], qq[e].x, d0);
+                            S[e][1] = fmaf(decay, S[e][1], kk[e].y * v); d1 = fmaf(S[e][1], qq[e].y, d1);
+                            S[e][2] = fmaf(decay, S[e][2], kk[e].z * v); d2 = fmaf(S[e][2], qq[e].z, d2);
+                            S[e][3] = fmaf(decay, S[e][3], kk[e].w * v); d3 = fmaf(S[e][3], qq[e].w, d3);
+                        }
+                    } else {
+                        const float g = gs[t], beta = bs[t];
+                        float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < E4; ++e) {
+                            S[e][0] *= g; c0 = fmaf(S[e][0], kk[e].x, c0);
+                            S[e][1] *= g; c1 = fmaf(S[e][1], kk[e].y, c1);
+                            S[e][2] *= g; c2 = fmaf(S[e][2], kk[e].z, c2);
+                            S[e][3] *= g; c3 = fmaf(S[e][3], kk[e].w, c3);
+                        }
+                        float dk = (c0 + c1) + (c2 + c3);
+                        dk += __shfl_xor_sync(0xffffffffu, dk, 1);
+                        dk += __shfl_xor_sync(0xffffffffu, dk, 2);
+                        dk += __shfl_xor_sync(0xffffffffu, dk, 4);
+                        const float u_t = beta * (v - dk);
+#pragma unroll
+                        for (int e = 0; e < E4; ++e) {
+                            S[e][0] = fmaf(kk[e].x, u_t, S[e][0]); d0 = fmaf(S[e][0], qq[e].x, d0);
+                            S[e][1] = fmaf(kk[e].y, u_t, S[e][1]); d1 = fmaf(S[e][1], qq[e].y, d1);
+                            S[e][2] = fmaf(kk[e].z, u_t, S[e][2]); d2 = fmaf(S[e][2], qq[e].z, d2);
+                            S[e][3] = fmaf(kk[e].w, u_t, S[e][3]); d3 = fmaf(S[e][3], qq[e].w, d3);
+                        }
+                    }
+                    dots[u] = (d0 + d1) + (d2 + d3);
+                }
             }
-            const float v = vs[t * kScanBlockCols + warp * kScanCols + (lane >> 3)];
-            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
-            if (s.rule == 0) {
 #pragma unroll
-                for (int e = 0; e < E4; ++e) {
-                    S[e][0] = fmaf(decay, S[e][0], kk[e].x * v); d0 = fmaf(S[e][0], qq[e].x, d0);
-                    S[e][1] = fmaf(decay, S[e][1], kk[e].y * v); d1 = fmaf(S[e][1], qq[e].y, d1);
-                    S[e][2] = fmaf(decay, S[e][2], kk[e].z * v); d2 = fmaf(S[e][2], qq[e].z, d2);
-                    S[e][3] = fmaf(decay, S[e][3], kk[e].w * v); d3 = fmaf(S[e][3], qq[e].w, d3);
-                }
-            } else {
-                const float g = gs[t], beta = bs[t];
-                float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+            for (int u = 0; u < 4; ++u) dots[u] += __shfl_xor_sync(0xffffffffu, dots[u], 1);
 #pragma unroll
-                for (int e = 0; e < E4; ++e) {
-                    S[e][0] *= g; c0 = fmaf(S[e][0], kk[e].x, c0);
-                    S[e][1] *= g; c1 = fmaf(S[e][1], kk[e].y, c1);
-                    S[e][2] *= g; c2 = fmaf(S[e][2], kk[e].z, c2);
-                    S[e][3] *= g; c3 = fmaf(S[e][3], kk[e].w, c3);
-                }
-                float dk = (c0 + c1) + (c2 + c3);
-                dk += __shfl_xor_sync(0xffffffffu, dk, 1);
-                dk += __shfl_xor_sync(0xffffffffu, dk, 2);
-                dk += __shfl_xor_sync(0xffffffffu, dk, 4);
-                const float u = beta * (v - dk);
+            for (int u = 0; u < 4; ++u) dots[u] += __shfl_xor_sync(0xffffffffu, dots[u], 2);
 #pragma unroll
-                for (int e = 0; e < E4; ++e) {
-                    S[e][0] = fmaf(kk[e].x, u, S[e][0]); d0 = fmaf(S[e][0], qq[e].x, d0);
-                    S[e][1] = fmaf(kk[e].y, u, S[e][1]); d1 = fmaf(S[e][1], qq[e].y, d1);
-                    S[e][2] = fmaf(kk[e].z, u, S[e][2]); d2 = fmaf(S[e][2], qq[e].z, d2);
-                    S[e][3] = fmaf(kk[e].w, u, S[e][3]); d3 = fmaf(S[e][3], qq[e].w, d3);
-                }
+            for (int u = 0; u < 4; ++u) dots[u] += __shfl_xor_sync(0xffffffffu, dots[u], 4);
+            if (sub == 0) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (t0 + u < n) os[(t0 + u) * kScanBlockCols + warp * kScanCols + (lane >> 3)] = dots[u];
             }
-            float dot = (d0 + d1) + (d2 + d3);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-            if (sub == 0) os[t * kScanBlockCols + warp * kScanCols + (lane >> 3)] = dot;
         }
         __syncthreads();
         for (int i = threadIdx.x; i < n * kScanBlockCols; i += blockDim.x) {
