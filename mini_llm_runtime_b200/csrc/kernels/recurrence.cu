@@ -26,6 +26,8 @@
 // inputs of every request kept as state; `mlr_short_conv_state` moves that state on after a step.
 #include "common.cuh"
 
+#include <type_traits>
+
 struct RecurrenceSpec {
     const float* freq;         // [rot_dims / 2] or null
     const float* decay;        // [heads] (rule 0)
@@ -481,7 +483,8 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
     const float decay = s.rule == 0 ? s.decay[head] : 1.0f;
 
     constexpr int kVPerThread = 32 * kScanBlockCols / (kScanWarps * 32);     // batch <= 32
-    float v_next[kVPerThread], g_next = 0.0f, b_next = 0.0f;
+    T v_next[kVPerThread];                // as loaded: a conversion right behind the load would wait for it
+    float g_next = 0.0f, b_next = 0.0f;
     // Starts the copies of a batch's q and k into a stage and loads its v, g and beta into registers.
     auto fetch = [&](int base, int into) {
         const int n = min(batch, count - base);
@@ -508,7 +511,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
         for (int j = 0; j < kVPerThread; ++j) {
             const int i = threadIdx.x + j * kScanWarps * 32;
             const int t = i / kScanBlockCols, c = block_col + i % kScanBlockCols;
-            v_next[j] = (t < n && c < s.vdim) ? mlr_load(proj + static_cast<size_t>(first + base + t) * ld, s.col_v + head * s.vdim + c) : 0.0f;
+            v_next[j] = proj[(t < n && c < s.vdim) ? static_cast<size_t>(first + base + t) * ld + s.col_v + head * s.vdim + c : 0];
         }
         if (s.rule == 1 && threadIdx.x < n) {
             g_next = __ldcg(gates + static_cast<size_t>(first + base + threadIdx.x) * 2 * s.heads + head);
@@ -524,7 +527,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
 #pragma unroll
         for (int j = 0; j < kVPerThread; ++j) {
             const int i = threadIdx.x + j * kScanWarps * 32;
-            if (i < batch * kScanBlockCols) vs[i] = v_next[j];
+            if (i < batch * kScanBlockCols) vs[i] = mlr_load(&v_next[j], 0);
         }
         if (threadIdx.x < batch) {
             gs[threadIdx.x] = g_next;
@@ -537,13 +540,13 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
         const float* know = ks + current * stage;
         // Four tokens at a time: their sums over a column are exchanged together, and nothing is stored to shared
         // memory in between (a store there would keep the next token's loads from starting early).
-        for (int t0 = 0; t0 < n; t0 += 4) {
+        auto walk4 = [&](int t0, auto guarded) {
             float dots[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int t = t0 + u;
                 dots[u] = 0.0f;
-                if (t < n) {
+                if (!decltype(guarded)::value || t < n) {
                     const float4* k4 = reinterpret_cast<const float4*>(know + static_cast<size_t>(t) * s.dim);
                     const float4* q4 = reinterpret_cast<const float4*>(qnow + static_cast<size_t>(t) * s.dim);
                     float4 kk[E4], qq[E4];
@@ -597,8 +600,12 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
             if (sub == 0) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
-                    if (t0 + u < n) os[(t0 + u) * kScanBlockCols + warp * kScanCols + (lane >> 3)] = dots[u];
+                    if (!decltype(guarded)::value || t0 + u < n) os[(t0 + u) * kScanBlockCols + warp * kScanCols + (lane >> 3)] = dots[u];
             }
+        };
+        for (int t0 = 0; t0 < n; t0 += 4) {
+            if (t0 + 4 <= n) walk4(t0, std::false_type{});      // whole groups carry no per-token conditions
+            else walk4(t0, std::true_type{});
         }
         __syncthreads();
         for (int i = threadIdx.x; i < n * kScanBlockCols; i += blockDim.x) {

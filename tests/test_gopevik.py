@@ -145,11 +145,12 @@ def test_grouped_norm_kernel(dtype, width, groups):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("activation", [0, 1])
-def test_gated_bias_kernel(activation):
+@pytest.mark.parametrize("inter", [37, 40, 1024])
+def test_gated_bias_kernel(activation, inter):
     from mini_llm_runtime_b200.ops import native
     dev = "cuda:0"
     g = torch.Generator().manual_seed(3)
-    rows, inter = 7, 37
+    rows = 7
     both = torch.randn(rows, 2 * inter, generator=g).to(dev)
     bg, bu = torch.randn(inter, generator=g).to(dev), torch.randn(inter, generator=g).to(dev)
     out = torch.empty(rows, inter, device=dev)
