@@ -151,12 +151,24 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
                     const T* k = cache + page * page_elems + (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.dim;
                     offset = static_cast<long long>(page * page_elems + key_plane +
                                                     (static_cast<size_t>(kv_head) * page_size + t % page_size) * s.vdim);
-                    for (int c = (threadIdx.x & 1) * kChunk; c < s.dim; c += 2 * kChunk) {
-                        float v[kChunk];
-                        if constexpr (sizeof(T) == 2) mlr_load8(k + c, v);
-                        else mlr_load4(k + c, v);
+                    for (int c0 = (threadIdx.x & 1) * kChunk; c0 < s.dim; c0 += 8 * kChunk) {     // four pieces on their way at a time
+                        float v[4][kChunk];
 #pragma unroll
-                        for (int e = 0; e < kChunk; ++e) partial = fmaf(qs[c + e], v[e], partial);
+                        for (int j = 0; j < 4; ++j) {
+                            const int c = c0 + j * 2 * kChunk;
+                            if (c < s.dim) {
+                                if constexpr (sizeof(T) == 2) mlr_load8(k + c, v[j]);
+                                else mlr_load4(k + c, v[j]);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int c = c0 + j * 2 * kChunk;
+                            if (c < s.dim) {
+#pragma unroll
+                                for (int e = 0; e < kChunk; ++e) partial = fmaf(qs[c + e], v[j][e], partial);
+                            }
+                        }
                     }
                 }
             }
@@ -605,7 +617,7 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
                                  int ldo, int act_bf16, const void* cache, int num_pages, const int* positions,
                                  const int* segment_of_row, const int* block_table, int table_stride, int page_size, int rows,
                                  const int* items, int n_items, const int* segment_info, int split_keys, int max_splits,
-                                 float* partial, int* status, cudaStream_t stream) {
+                                 int finer, float* partial, int* status, cudaStream_t stream) {
     // With `segment_info` the kernel runs over `n_items` segments of at most 16 rows each (`items` lists them; null: the
     // step's first n_items segments) and `rows` is not used; without it, over all `rows` rows.  With `partial` (float32,
     // n_items * 16 * kv_heads * max_splits * (vdim + 2), segments of at most 16 / (heads / kv_heads) rows) and more than
@@ -617,8 +629,20 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
         partial = nullptr;
         max_splits = 1;
     } else {
-        MLR_REQUIRE(split_keys >= kTile && split_keys % kTile == 0 && max_splits <= 65535, "attention_masked: bad key split %d x %d",
+        MLR_REQUIRE(split_keys >= kTile && split_keys % kTile == 0 && max_splits <= 65535 && finer >= 1, "attention_masked: bad key split %d x %d",
                     split_keys, max_splits);
+        // `finer`: the caller's `partial` has room for that many times `max_splits` ranges; each planned range is cut
+        // further (down to two tiles of keys) so that more blocks have loads in flight at once.
+        if (finer > 1) {
+            const long long span = static_cast<long long>(split_keys) * max_splits;
+            const int tiles = split_keys / kTile;
+            const int fewer = tiles / finer >= 2 ? (tiles + finer - 1) / finer : (tiles >= 2 ? 2 : tiles);    // tiles of a finer range
+            const long long ranges = (span + static_cast<long long>(fewer) * kTile - 1) / (static_cast<long long>(fewer) * kTile);
+            if (ranges <= static_cast<long long>(max_splits) * finer && ranges <= 65535) {
+                split_keys = fewer * kTile;
+                max_splits = static_cast<int>(ranges);
+            }
+        }
     }
     MLR_REQUIRE(rows >= 0 && page_size > 0 && num_pages > 0, "attention_masked: bad page size or page count");
     MLR_REQUIRE(ldq >= spec->heads * spec->dim && ldo >= spec->heads * spec->vdim, "attention_masked: a row stride is smaller than the row");

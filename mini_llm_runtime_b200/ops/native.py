@@ -91,7 +91,7 @@ _SIGNATURES = {
         "mlr_kv_rope_cache": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                               c_int, c_int, c_void_p, c_void_p],
         "mlr_attention_masked": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+                                 c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "mlr_attention_masked_tiles_fit": [c_int, c_int],
         "mlr_attention_masked_tiles": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                        c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],

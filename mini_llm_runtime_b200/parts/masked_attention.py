@@ -31,6 +31,8 @@ from .base import CacheNeed, RunContext, SequenceCore, columns_of
 
 
 class MaskedAttentionMixer(SequenceCore):
+    FINER = 4       # how much finer than the step's plan the row kernel cuts long contexts (see emit_core)
+
     def __init__(self, spec):
         super().__init__(spec)
         p = spec.params
@@ -99,17 +101,21 @@ class MaskedAttentionMixer(SequenceCore):
         if not tiled:
             # One block per (row, head): the float32 path, and sizes the tiled kernel does not take.
             b.launch("attention_masked", "mlr_attention_masked", *args, proj.is_bf16, *where, b.meta("positions"),
-                     b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, 0, 1, None, b.status, b.stream)
+                     b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, 0, 1, 1, None, b.status, b.stream)
             return
         # The step's launch plan (made by the native executor from the step's segments, shared by all layers):
         # segments of few rows (a decoded token, a short portion) go to the row kernel, prompt portions in tiles of 64
         # rows to the tensor-core kernel.
         # The row kernel cuts long contexts into key ranges that run as blocks of their own (the plan's split of the keys and
         # its scratch for the ranges' partial results: 16 rows x kv heads x splits x (head size + 2) floats per segment).
+        # The planner sizes the scratch by the head size it is told: FINER times the room of a range's (value size + 2)
+        # floats lets the kernel cut every planned range into FINER (its blocks wait for memory most of the time, and
+        # more of them in flight is what makes a long context fast; the planner's own split is tuned for a kernel that
+        # copies keys in bulk).
         group = self.heads // self.kv_heads
-        plan = b.plan((group if group <= 16 else 1, self.kv_heads, 0, 0, max(self.dim, self.vdim), 1))
+        plan = b.plan((group if group <= 16 else 1, self.kv_heads, 0, 0, self.FINER * (max(self.dim, self.vdim) + 2), 1))
         info = b.meta("segment_info")
-        split = (plan.chunk, plan.max_splits, plan.scratch) if group <= 16 else (0, 1, None)
+        split = (plan.chunk, plan.max_splits, self.FINER, plan.scratch) if group <= 16 else (0, 1, 1, None)
         b.launch("attention_masked", "mlr_attention_masked", *args, 1, *where, b.meta("positions"), b.meta("segment_of_row"), table,
                  stride, b.page_size, 0, plan.items, plan.n_items, info, *split, b.status, b.stream, need=plan.n_items)
         b.launch("attention_masked", "mlr_attention_masked_tiles", *args, *where, plan.tiles, plan.n_tiles, info, table, stride,

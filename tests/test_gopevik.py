@@ -205,15 +205,16 @@ def _attention_case(dtype, heads, kv_heads, dim, vdim, rot_dims, factor, chunk, 
         _call("attention_masked", "mlr_attention_masked_tiles", *common, cache.data_ptr(), n_pages, tiles.data_ptr(), tiles.shape[0],
               info.data_ptr(), two.data_ptr(), two.stride(0), page, status.data_ptr(), native.stream())
     elif split:     # the last rows as a segment of few rows, its keys cut into ranges that are added up afterwards
-        last, keys, most = split
+        last, keys, most = split[:3]
+        finer = split[3] if len(split) > 3 else 1
         info = torch.tensor([[T - last, last, T - last, 0]], dtype=torch.int32, device=dev)
-        partial = torch.full((16 * kv_heads * most * (vdim + 2),), float("nan"), device=dev)
+        partial = torch.full((16 * kv_heads * most * finer * (vdim + 2),), float("nan"), device=dev)
         _call("attention_masked", "mlr_attention_masked", *common, is16, cache.data_ptr(), n_pages, positions.data_ptr(),
-              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, 0, None, 1, info.data_ptr(), keys, most, partial.data_ptr(),
+              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, 0, None, 1, info.data_ptr(), keys, most, finer, partial.data_ptr(),
               status.data_ptr(), native.stream())
     else:
         _call("attention_masked", "mlr_attention_masked", *common, is16, cache.data_ptr(), n_pages, positions.data_ptr(),
-              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, None, 0, None, 0, 1, None, status.data_ptr(), native.stream())
+              of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, None, 0, None, 0, 1, 1, None, status.data_ptr(), native.stream())
     assert int(status.item()) == 0
     pos = torch.arange(T)
     qd = plain.rotate_half(q.double().cpu().view(T, heads, dim), pos, rot_dims, base, factor) if rot_dims else q.double().cpu().view(T, heads, dim)
@@ -283,6 +284,8 @@ def test_masked_attention_in_tiles_on_the_tensor_cores(case):
     dict(heads=2, kv_heads=2, dim=16, vdim=40, rot_dims=16, factor=2.0, chunk=300, window=None, sink=True, gate=None, T=650, page=8, split=(8, 64, 11)),
     dict(heads=3, kv_heads=1, dim=8, vdim=8, rot_dims=0, factor=1.0, chunk=None, window=None, sink=False, gate="silu", T=333, page=16, split=(1, 192, 2)),
     dict(heads=1, kv_heads=1, dim=32, vdim=200, rot_dims=4, factor=1.0, chunk=100, window=None, sink=True, gate=None, T=402, page=16, split=(16, 64, 7)),
+    dict(heads=2, kv_heads=1, dim=16, vdim=24, rot_dims=8, factor=1.0, chunk=None, window=None, sink=True, gate="sigmoid", T=1500, page=16, split=(3, 512, 3, 4)),
+    dict(heads=2, kv_heads=2, dim=8, vdim=8, rot_dims=0, factor=1.0, chunk=900, window=None, sink=False, gate=None, T=1000, page=16, split=(2, 384, 3, 4)),
 ])
 def test_masked_attention_with_the_keys_cut_into_ranges(dtype, case):
     got, want = _attention_case(dtype, **case)
