@@ -88,14 +88,17 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     float* qs = scores + kTile;                                  // [dim]
     __shared__ int bad;
 
-    int row = blockIdx.x;
-    if (segment_info) {         // blockIdx.x = (segment of few rows, row of it); `items` lists those segments, or all are
-        const int item = blockIdx.x / kRowsPerItem, j = blockIdx.x % kRowsPerItem;
-        const int* info = segment_info + 4 * (items ? items[item] : item);
-        if (j >= info[1]) return;
-        row = info[0] + j;
+    // With `segment_info`, blockIdx.x names a segment of few rows (`items` lists those segments, or all are) and the block
+    // walks its rows one after the other; without, blockIdx.x is the row.
+    int first_row = blockIdx.x, n_rows = 1;
+    if (segment_info) {
+        const int* info = segment_info + 4 * (items ? items[blockIdx.x] : blockIdx.x);
+        first_row = info[0];
+        n_rows = min(info[1], kRowsPerItem);
     }
     const int head = blockIdx.y;
+    auto one_row = [&](const int row, const int j) {
+    __syncthreads();            // the row before is done with the shared memory
     const int kv_head = head / (s.heads / s.kv_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int position = positions[row];
@@ -238,11 +241,9 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
         }
         __syncthreads();
     }
-    mlr_grid_dependents_may_start();
     if (bad && threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
     if (partial) {
-        const int j = blockIdx.x % kRowsPerItem;
-        float* mine = partial + ((static_cast<size_t>(blockIdx.x / kRowsPerItem) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits +
+        float* mine = partial + ((static_cast<size_t>(blockIdx.x) * kRowsPerItem * s.kv_heads + j * s.heads + head) * max_splits +
                                  blockIdx.z) * (s.vdim + 2);
         if (threadIdx.x == 0) {
             mine[0] = running_max;
@@ -270,17 +271,20 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
             mlr_store(orow, c, value * s.out_scale);
         }
     }
+    };
+    for (int j = 0; j < n_rows; ++j) one_row(first_row + j, j);
+    mlr_grid_dependents_may_start();
 }
 
-// Adds up the key ranges of a row: grid (segments of few rows * 16, heads), as the row kernel's.
+// Adds up the key ranges of every row of a segment: grid (segments of few rows, heads), as the row kernel's.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const float* partial, const T* gate, int ld_gate, T* out, int ldo,
                                                                           const int* positions, MaskedAttentionSpec s, const int* items,
                                                                           const int* segment_info, int split_keys, int max_splits) {
     mlr_grid_wait();
-    const int item = blockIdx.x / kRowsPerItem, j = blockIdx.x % kRowsPerItem, head = blockIdx.y;
+    const int item = blockIdx.x, head = blockIdx.y;
     const int* info = segment_info + 4 * (items ? items[item] : item);
-    if (j >= info[1]) return;
+    for (int j = 0; j < min(info[1], kRowsPerItem); ++j) {
     const int row = info[0] + j;
     const int position = positions[row];
     int lo = 0;
@@ -318,6 +322,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
             }
             mlr_store(orow, c, value * s.out_scale);
         }
+    }
     }
     mlr_grid_dependents_may_start();
 }
@@ -624,7 +629,7 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
     // one split, every row's keys are cut into ranges of `split_keys` that run as blocks of their own, and a second
     // kernel adds the ranges up.
     if (check_spec(spec, "attention_masked")) return 1;
-    if (segment_info) rows = n_items * kRowsPerItem;
+    if (segment_info) rows = n_items;          // a block per segment; it walks the segment's rows
     if (!partial || max_splits <= 1 || !segment_info) {
         partial = nullptr;
         max_splits = 1;
