@@ -10,7 +10,7 @@ module only translates its own config.json into one.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Tuple, Union
 
 
 class ConfigError(ValueError):
@@ -35,9 +35,10 @@ class LayerSpec:
     """One layer: a block arrangement around a mixer and a feed-forward.
 
     `norms` maps the arrangement's norm slots (for the pre-norm block:
-    "pre_mixer", "pre_feed_forward") to norm specs.
+    "pre_mixer", "pre_feed_forward") to norm specs.  `block` is the arrangement's registered
+    kind, or a `PartSpec` when the arrangement has parameters and weights of its own.
     """
-    block: str
+    block: Union[str, PartSpec]
     mixer: PartSpec
     feed_forward: Optional[PartSpec]      # None: the layer has no feed-forward (its block must know)
     norms: Dict[str, PartSpec]

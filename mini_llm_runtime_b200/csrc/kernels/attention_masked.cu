@@ -11,7 +11,7 @@
 //   gate:       out *= sigmoid(gate) or silu(gate), element by element, and a constant factor
 //
 // Cache of a layer: per page, the keys [kv_head][token_in_page][dim] and then the values
-// [kv_head][token_in_page][vdim].  `mlr_kv_rope_cache` rotates the step's keys and writes keys and
+// [kv_head][token_in_page][vdim] (with shared_kv only the keys, which are the values too).  `mlr_kv_rope_cache` rotates the step's keys and writes keys and
 // values; `mlr_attention_masked` rotates its query as it loads it and walks the visible keys in tiles
 // of 64 with a running maximum, one block per (row, query head), so a row's result depends on its
 // position and on the cache only.  Scores, weights and sums are float32; q, the cache, the gate and
@@ -25,6 +25,7 @@ struct MaskedAttentionSpec {
     int heads, kv_heads, dim, vdim;
     int rot_dims, window, chunk, sink;
     int gate_kind;         // 0 none, 1 sigmoid, 2 silu
+    int shared_kv;         // 1: a token's value IS its key (vdim == dim; one vector per token is cached and a page holds keys only)
     float scale, out_scale;
 };
 
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
         if (threadIdx.x == 0 && status) atomicOr(status, MLR_STATUS_BAD_PAGE);
         return;
     }
-    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.dim + s.vdim);
+    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
     T* kbase = cache + page * page_elems + static_cast<size_t>(position % page_size) * s.dim;
     T* vbase = cache + page * page_elems + static_cast<size_t>(s.kv_heads) * page_size * s.dim +
                static_cast<size_t>(position % page_size) * s.vdim;
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
         }
         mlr_store(kbase + static_cast<size_t>(head) * page_size * s.dim, c, value);
     }
-    for (int i = threadIdx.x; i < s.kv_heads * s.vdim; i += kThreads) {
+    for (int i = threadIdx.x; i < (s.shared_kv ? 0 : s.kv_heads * s.vdim); i += kThreads) {
         const int head = i / s.vdim, c = i % s.vdim;
         vbase[static_cast<size_t>(head) * page_size * s.vdim + c] = vrow[i];
     }
@@ -107,8 +108,8 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     if (s.window > 0) lo = max(lo, position - s.window + 1);
     if (s.chunk > 0) lo = max(lo, (position / s.chunk) * s.chunk);
     const int* table = block_table + static_cast<size_t>(segment) * table_stride;
-    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.dim + s.vdim);
-    const size_t key_plane = static_cast<size_t>(s.kv_heads) * page_size * s.dim;
+    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
+    const size_t key_plane = s.shared_kv ? 0 : static_cast<size_t>(s.kv_heads) * page_size * s.dim;
 
     const T* qrow = q + static_cast<size_t>(row) * ldq + static_cast<size_t>(head) * s.dim;
     const int half = s.rot_dims / 2;
@@ -384,8 +385,8 @@ __global__ void __launch_bounds__(128) attention_masked_tile_kernel(const __nv_b
     const int lo_min = first_visible(first_pos, s);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int* table = block_table + static_cast<size_t>(segment) * table_stride;
-    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.dim + s.vdim);
-    const size_t key_plane = static_cast<size_t>(s.kv_heads) * page_size * s.dim;
+    const size_t page_elems = static_cast<size_t>(s.kv_heads) * page_size * (s.shared_kv ? s.dim : s.dim + s.vdim);
+    const size_t key_plane = s.shared_kv ? 0 : static_cast<size_t>(s.kv_heads) * page_size * s.dim;
     if (threadIdx.x == 0) bad = 0;
 
     // The block's queries, rotated in float32, as bfloat16.
@@ -595,6 +596,7 @@ int check_spec(const MaskedAttentionSpec* s, const char* who) {
     MLR_REQUIRE(s->rot_dims >= 0 && s->rot_dims % 2 == 0 && s->rot_dims <= s->dim && (s->rot_dims == 0 || s->freq),
                 "%s: %d rotated values do not fit a head of %d (or no frequencies were given)", who, s->rot_dims, s->dim);
     MLR_REQUIRE(s->window >= 0 && s->chunk >= 0 && s->heads <= 65535, "%s: bad window, chunk or head count", who);
+    MLR_REQUIRE(!s->shared_kv || s->vdim == s->dim, "%s: values that are the keys have the keys' size, not %d against %d", who, s->vdim, s->dim);
     return 0;
 }
 

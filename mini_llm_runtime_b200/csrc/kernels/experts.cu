@@ -1,0 +1,311 @@
+// Routed experts: a feed-forward made of many small gated feed-forwards of which every token uses a few.
+//
+//   route     per token, float32: z = R x (R [experts, width] float32), s = sigmoid(z), choice = s + correction;
+//             experts form `groups` equal groups of neighbours, a group's score is the sum of its two largest
+//             choices, only experts of the `keep` best groups can be chosen (`top` of them, by choice, ties to
+//             the lower index); weights = s of the chosen over their sum (+ 1e-20).  One more row of R, if given,
+//             is the gate of a shared expert: sigmoid of its product, one number per token.  The kernel also
+//             counts the tokens of every expert (a token's place among its expert's tokens is the count it met).
+//   arrange   one block: running sums of the counts (first row of every expert in the order by expert), the
+//             list of row tiles for the products, each (token, choice) pair's row in that order and back;
+//             the counts are zero again afterwards.
+//   products  over the rows in the order by expert, a tile of rows of ONE expert per block, the rows of the
+//             first product gathered from the tokens' activations:  act = silu(x Wg_e^T) .* (x Wu_e^T), then
+//             y = act Wd_e^T in float32.  Every output adds its K products in the order k = 0 .. K-1 in float32,
+//             so a token's result does not depend on which other tokens share its tile.
+//   combine   out[token] = sum_j weight_j y[row of (token, j)]  (+ shared gate * shared expert's result), j in
+//             the order of the choice.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRouteThreads = 128;
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxTop = 32;
+constexpr int kTileRows = 32;     // rows of one expert per block of a product
+constexpr int kTileCols = 64;
+constexpr int kTileK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long long ld, const float* router, const float* correction,
+                                                              int width, int experts, int groups, int keep, int top, int has_gate,
+                                                              int* chosen, float* weights, int* place, int* counts, float* shared_gate) {
+    mlr_grid_wait();
+    extern __shared__ __align__(16) float shared[];
+    float* xs = shared;                 // [width]
+    float* score = xs + width;          // [experts] plain scores
+    float* choice = score + experts;    // [experts] scores with the correction (minus infinity once taken or not allowed)
+    float* group_score = choice + experts;   // [groups]
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kRouteThreads / 32;
+    const T* xrow = x + static_cast<size_t>(row) * ld;
+    for (int c = threadIdx.x; c < width; c += kRouteThreads) xs[c] = mlr_load(xrow, c);
+    __syncthreads();
+    for (int e = warp; e < experts + has_gate; e += warps) {
+        const float* w = router + static_cast<size_t>(e) * width;
+        float sum = 0.0f;
+        for (int c = lane; c < width; c += 32) sum = fmaf(w[c], xs[c], sum);
+        sum = mlr_warp_sum(sum);
+        if (lane == 0) {
+            const float s = 1.0f / (1.0f + expf(-sum));
+            if (e < experts) {
+                score[e] = s;
+                choice[e] = s + (correction ? correction[e] : 0.0f);
+            } else {
+                shared_gate[row] = s;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const float none = -INFINITY;
+    const int per = experts / groups;
+    if (groups > 1 && keep < groups) {
+        for (int g = 0; g < groups; ++g) {
+            float a = none, b = none;           // the two largest of the group
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = choice[e];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            group_score[g] = per > 1 ? a + b : a;
+        }
+        // Groups outside the `keep` best lose their experts: mark the kept ones by taking them out of group_score.
+        for (int k = 0; k < keep; ++k) {
+            int best = -1;
+            float value = none;
+            for (int g = 0; g < groups; ++g)
+                if (!isnan(group_score[g]) && (best < 0 || group_score[g] > value)) { best = g; value = group_score[g]; }
+            group_score[best] = NAN;            // NaN marks a kept group
+        }
+        for (int g = 0; g < groups; ++g)
+            if (!isnan(group_score[g]))
+                for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = none;
+    }
+    float picked[kMaxTop];
+    float total = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        int best = 0;
+        float value = none;
+        bool found = false;
+        for (int e = 0; e < experts; ++e)
+            if (!isnan(choice[e]) && (!found || choice[e] > value)) { best = e; value = choice[e]; found = true; }
+        choice[best] = NAN;                     // NaN marks a taken expert
+        chosen[static_cast<size_t>(row) * top + k] = best;
+        picked[k] = score[best];
+        total += score[best];
+        place[static_cast<size_t>(row) * top + k] = atomicAdd(counts + best, 1);
+    }
+    for (int k = 0; k < top; ++k) weights[static_cast<size_t>(row) * top + k] = picked[k] / (total + 1e-20f);
+}
+
+// One block.  first_row [experts + 1]; tiles: {expert, first row, rows} per tile, n_tiles[0] their number; row_of_pair [pairs]
+// (the row of pair = token * top + choice in the order by expert), pair_of_row [pairs] the other way.
+__global__ void __launch_bounds__(1024) arrange_kernel(int* counts, const int* chosen, const int* place, int experts, int pairs,
+                                                       int* first_row, int* tiles, int* n_tiles, int* row_of_pair, int* pair_of_row) {
+    mlr_grid_wait();
+    __shared__ int first[kMaxExperts + 1];
+    __shared__ int first_tile[kMaxExperts + 1];
+    if (threadIdx.x == 0) {
+        int rows = 0, t = 0;
+        for (int e = 0; e < experts; ++e) {
+            first[e] = rows;
+            first_tile[e] = t;
+            rows += counts[e];
+            t += (counts[e] + kTileRows - 1) / kTileRows;
+        }
+        first[experts] = rows;
+        first_tile[experts] = t;
+        n_tiles[0] = t;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) first_row[e] = first[e];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int n = first[e + 1] - first[e];
+        for (int t = first_tile[e], r = 0; r < n; ++t, r += kTileRows) {
+            tiles[3 * t] = e;
+            tiles[3 * t + 1] = first[e] + r;
+            tiles[3 * t + 2] = min(kTileRows, n - r);
+        }
+        counts[e] = 0;
+    }
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int row = first[chosen[p]] + place[p];
+        row_of_pair[p] = row;
+        pair_of_row[row] = p;
+    }
+}
+
+// C tile = A tile (rows of one expert, gathered through `source` / divisor when given) times W_e^T, W_e [N, K] at w + e * N * K.
+// DUAL: two matrices (gate and up) and out = silu(gate) * up in TO; else the product itself in TO.
+template <typename T, typename TO, bool DUAL>
+__global__ void __launch_bounds__(256) expert_product_kernel(const T* a, long long lda, const int* source, int divisor, const T* w, const T* w2,
+                                                             int N, int K, TO* out, long long ldo, const int* tiles, const int* n_tiles) {
+    mlr_grid_wait();
+    const int tile = blockIdx.y;
+    if (tile >= __ldcg(n_tiles)) return;
+    const int expert = __ldcg(tiles + 3 * tile), row0 = __ldcg(tiles + 3 * tile + 1), rows = __ldcg(tiles + 3 * tile + 2);
+    const int col0 = blockIdx.x * kTileCols;
+    __shared__ float As[kTileK][kTileRows + 1];
+    __shared__ float Ws[kTileK][kTileCols + 1];
+    __shared__ float W2s[DUAL ? kTileK : 1][kTileCols + 1];
+    __shared__ long long arow[kTileRows];
+    if (threadIdx.x < kTileRows) {
+        const int r = row0 + min(static_cast<int>(threadIdx.x), rows - 1);
+        arow[threadIdx.x] = static_cast<long long>(source ? __ldcg(source + r) / divisor : r) * lda;
+    }
+    __syncthreads();
+    const T* we = w + static_cast<size_t>(expert) * N * K;
+    const T* we2 = DUAL ? w2 + static_cast<size_t>(expert) * N * K : nullptr;
+    // 256 threads: thread (ty, tx) = (threadIdx.x / 16, threadIdx.x % 16) owns rows ty * 2 + {0, 1} and columns tx + 16 * {0..3}.
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[2][4] = {}, acc2[DUAL ? 2 : 1][4] = {};
+    for (int k0 = 0; k0 < K; k0 += kTileK) {
+        for (int i = threadIdx.x; i < kTileRows * kTileK; i += 256) {
+            const int r = i / kTileK, k = i % kTileK;
+            As[k][r] = k0 + k < K ? mlr_load(a + arow[r], k0 + k) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < kTileCols * kTileK; i += 256) {
+            const int c = i / kTileK, k = i % kTileK;
+            const bool in = col0 + c < N && k0 + k < K;
+            Ws[k][c] = in ? mlr_load(we, static_cast<size_t>(col0 + c) * K + k0 + k) : 0.0f;
+            if (DUAL) W2s[k][c] = in ? mlr_load(we2, static_cast<size_t>(col0 + c) * K + k0 + k) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kTileK; ++k) {
+            const float a0 = As[k][2 * ty], a1 = As[k][2 * ty + 1];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float b = Ws[k][tx + 16 * j];
+                acc[0][j] = fmaf(a0, b, acc[0][j]);
+                acc[1][j] = fmaf(a1, b, acc[1][j]);
+                if (DUAL) {
+                    const float b2 = W2s[k][tx + 16 * j];
+                    acc2[0][j] = fmaf(a0, b2, acc2[0][j]);
+                    acc2[1][j] = fmaf(a1, b2, acc2[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    mlr_grid_dependents_may_start();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = 2 * ty + i;
+        if (r >= rows) continue;
+        TO* orow = out + static_cast<size_t>(row0 + r) * ldo;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = col0 + tx + 16 * j;
+            if (c >= N) continue;
+            float value = acc[i][j];
+            if (DUAL) value = value / (1.0f + expf(-value)) * acc2[i][j];
+            mlr_store(orow, c, value);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) combine_kernel(const float* y, long long ldy, const int* row_of_pair, const float* weights, int top,
+                                                      const T* shared_y, long long ld_shared, const float* shared_gate, float* out,
+                                                      long long ldo, int width) {
+    mlr_grid_wait();
+    const int row = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += 256) {
+        float sum = 0.0f;
+        for (int j = 0; j < top; ++j) {
+            const int p = row * top + j;
+            sum = fmaf(__ldcg(weights + p), __ldcg(y + static_cast<size_t>(__ldcg(row_of_pair + p)) * ldy + c), sum);
+        }
+        if (shared_y) {
+            const float v = mlr_load(shared_y + static_cast<size_t>(row) * ld_shared, c);
+            sum = shared_gate ? fmaf(__ldcg(shared_gate + row), v, sum) : sum + v;
+        }
+        out[static_cast<size_t>(row) * ldo + c] = sum;
+    }
+    mlr_grid_dependents_may_start();
+}
+
+}  // namespace
+
+// router: float32 [experts (+ 1 with has_gate), width]; correction: float32 [experts] or null; counts: int32 [experts], zero before
+// the call (`mlr_experts_arrange` zeroes them again).  chosen, place: int32 [rows, top]; weights: float32 [rows, top]; shared_gate [rows].
+MLR_API int mlr_experts_route(const void* x, long long ld, int act_bf16, const float* router, const float* correction, int rows, int width,
+                              int experts, int groups, int keep, int top, int has_gate, int* chosen, float* weights, int* place, int* counts,
+                              float* shared_gate, cudaStream_t stream) {
+    MLR_REQUIRE(x && router && chosen && weights && place && counts && width > 0, "experts_route: bad arguments");
+    MLR_REQUIRE(experts >= 1 && experts <= kMaxExperts && top >= 1 && top <= kMaxTop && top <= experts, "experts_route: %d of %d experts (at most %d of %d)",
+                top, experts, kMaxTop, kMaxExperts);
+    MLR_REQUIRE(groups >= 1 && experts % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (experts / groups),
+                "experts_route: %d experts in %d groups of which %d are kept cannot give %d", experts, groups, keep, top);
+    MLR_REQUIRE(!has_gate || shared_gate, "experts_route: no room for the shared expert's gate");
+    if (rows <= 0) return 0;
+    const size_t shared = sizeof(float) * (static_cast<size_t>(width) + 2 * experts + groups);
+    MLR_REQUIRE(shared <= 200 * 1024, "experts_route: a row of %d values and %d experts do not fit shared memory", width, experts);
+    if (act_bf16) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        mlr_launch((route_kernel<__nv_bfloat16>), dim3(rows), dim3(kRouteThreads), shared, stream, static_cast<const __nv_bfloat16*>(x), ld, router,
+                   correction, width, experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate);
+    } else {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        mlr_launch((route_kernel<float>), dim3(rows), dim3(kRouteThreads), shared, stream, static_cast<const float*>(x), ld, router, correction, width,
+                   experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate);
+    }
+    return mlr_launched("experts_route");
+}
+
+// tiles: int32 [3 * (pairs / 32 + experts)]; first_row: int32 [experts + 1]; n_tiles: int32 [1]; row_of_pair, pair_of_row: int32 [pairs].
+MLR_API int mlr_experts_arrange(int* counts, const int* chosen, const int* place, int experts, int rows, int top, int* first_row, int* tiles,
+                                int* n_tiles, int* row_of_pair, int* pair_of_row, cudaStream_t stream) {
+    MLR_REQUIRE(counts && chosen && place && first_row && tiles && n_tiles && row_of_pair && pair_of_row && experts >= 1 && experts <= kMaxExperts,
+                "experts_arrange: bad arguments");
+    if (rows <= 0) return 0;
+    mlr_launch(arrange_kernel, dim3(1), dim3(1024), 0, stream, counts, chosen, place, experts, rows * top, first_row, tiles, n_tiles, row_of_pair,
+               pair_of_row);
+    return mlr_launched("experts_arrange");
+}
+
+// The most tiles `pairs` rows of `experts` experts can make (the size of the grid, and of `tiles` / 3).
+MLR_API int mlr_experts_max_tiles(int pairs, int experts) { return pairs / kTileRows + experts; }
+
+// a: [*, K] activations (bfloat16 or float32), row r of the product is row source[r] / divisor of `a` (or r without `source`).
+// w (and w2 when `gated`): [experts, N, K] in the activations' precision.  out: [pairs, N]; float32 when out_f32, else the
+// activations' precision; with `gated` out = silu(a w^T) * (a w2^T).  The product has rows * top rows.
+MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, const int* source, int divisor, const void* w, const void* w2, int gated,
+                                int N, int K, void* out, long long ldo, int out_f32, const int* tiles, const int* n_tiles, int rows, int top, int experts,
+                                cudaStream_t stream) {
+    const int pairs = rows * top;
+    MLR_REQUIRE(a && w && out && tiles && n_tiles && N > 0 && K > 0 && (!gated || w2) && (!source || divisor > 0), "experts_product: bad arguments");
+    if (pairs <= 0) return 0;
+    const int max_tiles = mlr_experts_max_tiles(pairs, experts);
+    MLR_REQUIRE(max_tiles <= 65535, "experts_product: %d row tiles are more than a grid takes", max_tiles);
+    const dim3 grid((N + kTileCols - 1) / kTileCols, max_tiles);
+#define MLR_GO(T, TO, DUAL)                                                                                                              \
+    mlr_launch((expert_product_kernel<T, TO, DUAL>), dim3(grid), dim3(256), 0, stream, static_cast<const T*>(a), lda, source, divisor,   \
+               static_cast<const T*>(w), static_cast<const T*>(w2), N, K, static_cast<TO*>(out), ldo, tiles, n_tiles)
+    if (act_bf16) {
+        if (gated && !out_f32) MLR_GO(__nv_bfloat16, __nv_bfloat16, true);
+        else if (!gated && out_f32) MLR_GO(__nv_bfloat16, float, false);
+        else return mlr_fail("experts_product: this pair of precisions is not built");
+    } else {
+        if (gated) MLR_GO(float, float, true);
+        else MLR_GO(float, float, false);
+    }
+#undef MLR_GO
+    return mlr_launched("experts_product");
+}
+
+MLR_API int mlr_experts_combine(const float* y, long long ldy, const int* row_of_pair, const float* weights, int top, const void* shared_y,
+                                long long ld_shared, int shared_bf16, const float* shared_gate, float* out, long long ldo, int rows, int width,
+                                cudaStream_t stream) {
+    MLR_REQUIRE(y && row_of_pair && weights && out && top >= 1 && width > 0, "experts_combine: bad arguments");
+    if (rows <= 0) return 0;
+    if (shared_bf16)
+        mlr_launch((combine_kernel<__nv_bfloat16>), dim3(rows), dim3(256), 0, stream, y, ldy, row_of_pair, weights, top,
+                   static_cast<const __nv_bfloat16*>(shared_y), ld_shared, shared_gate, out, ldo, width);
+    else
+        mlr_launch((combine_kernel<float>), dim3(rows), dim3(256), 0, stream, y, ldy, row_of_pair, weights, top,
+                   static_cast<const float*>(shared_y), ld_shared, shared_gate, out, ldo, width);
+    return mlr_launched("experts_combine");
+}

@@ -2,6 +2,7 @@
 // float32, that every token updates and reads.  One kernel serves the family; what varies between
 // designs is a description in host memory (`RecurrenceSpec`):
 //
+//   activation of q, k and v as they are loaded (in_act): none, or SiLU
 //   preparation of q and k (float32, from the projections' output):
 //       rotate:  the first rot_dims values turned by position * freq[i] (value i paired with i + rot_dims/2)
 //       unit:    x / sqrt(sum(x^2) + unit_eps)
@@ -13,7 +14,8 @@
 //                columns of the projections' output per head
 //   (q, k, v come from one buffer, `proj`; a, b and the gate from another, `side`, which may be the same)
 //   read-out:    o / sqrt(mean(o^2) + eps) per head, times a weight [vdim] (optional), times silu(gate)
-//                or sigmoid(gate) (optional), times a constant
+//                or sigmoid(gate) (optional), times a constant; with norm_all the root mean square is taken over
+//                the outputs of all heads of a token together and the weight is [heads * vdim]
 //
 // The columns of S are independent of one another in both rules, so a warp owns a few columns (lanes
 // split `dim`), and one block owns one (request, head): it prepares a batch of tokens in shared memory,
@@ -41,17 +43,20 @@ struct RecurrenceSpec {
     int gate_kind;             // 0 none, 1 sigmoid, 2 silu
     int col_q, col_k, col_v;           // first columns of q, k, v in `proj`
     int col_a, col_b, col_gate;        // first columns of the rule's two inputs and of the gate in `side`
+    int in_act;                        // 0: q, k, v as projected; 1: through SiLU
+    int norm_all;                      // 0: the read-out norms every head alone; 1: all heads of a token together
     float q_mult, k_mult, unit_eps, eps, out_scale;
 };
 
 namespace {
 
 __device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float act_in(float x, int kind) { return kind == 1 ? x / (1.0f + expf(-x)) : x; }
 
 template <typename T, int R, int COLS>
 __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, int ld, const T* side, int ld_side, T* out, int ld_out, float* state,
                                                                   long long state_stride, const int* segment_info, RecurrenceSpec s,
-                                                                  int batch) {
+                                                                  int batch, float* raw) {
     mlr_grid_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     float* qs = reinterpret_cast<float*>(smem);          // [batch][dim]
@@ -87,12 +92,12 @@ __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, 
         for (int i = threadIdx.x; i < n * s.dim; i += threads) {
             const int t = i / s.dim, c = i % s.dim;
             const T* row = proj + static_cast<size_t>(first + base + t) * ld;
-            qs[i] = mlr_load(row, s.col_q + qk_head * s.dim + c);
-            ks[i] = mlr_load(row, s.col_k + qk_head * s.dim + c);
+            qs[i] = act_in(mlr_load(row, s.col_q + qk_head * s.dim + c), s.in_act);
+            ks[i] = act_in(mlr_load(row, s.col_k + qk_head * s.dim + c), s.in_act);
         }
         for (int i = threadIdx.x; i < n * s.vdim; i += threads) {
             const int t = i / s.vdim, c = i % s.vdim;
-            vs[i] = mlr_load(proj + static_cast<size_t>(first + base + t) * ld, s.col_v + head * s.vdim + c);
+            vs[i] = act_in(mlr_load(proj + static_cast<size_t>(first + base + t) * ld, s.col_v + head * s.vdim + c), s.in_act);
         }
         if (s.rule == 1 && threadIdx.x < n) {
             const T* row = side + static_cast<size_t>(first + base + threadIdx.x) * ld_side;
@@ -197,9 +202,14 @@ __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, 
             }
         }
         __syncthreads();
-        // ---- read-out of the batch: norm per head, weight, gate
+        // ---- read-out of the batch: norm per head, weight, gate; or the plain float32 outputs for a read-out kernel
         for (int t = warp; t < n; t += warps) {
             const float* o = os + static_cast<size_t>(t) * s.vdim;
+            if (raw) {
+                float* rrow = raw + (static_cast<size_t>(first + base + t) * s.heads + head) * s.vdim;
+                for (int c = lane; c < s.vdim; c += 32) rrow[c] = o[c];
+                continue;
+            }
             float inv = 1.0f;
             if (s.eps >= 0.0f) {
                 float sum = 0.0f;
@@ -257,21 +267,21 @@ __global__ void __launch_bounds__(128) recurrence_prepare_kernel(const T* proj, 
             for (int c = lane; c < half; c += 32) {
                 float sn, cs;
                 sincosf(position * s.freq[c], &sn, &cs);
-                const float u = mlr_load(x, c), v = mlr_load(x, c + half);
+                const float u = act_in(mlr_load(x, c), s.in_act), v = act_in(mlr_load(x, c + half), s.in_act);
                 y[c] = (u * cs - v * sn) * mult;
                 y[c + half] = (v * cs + u * sn) * mult;
             }
-            for (int c = s.rot_dims + lane; c < s.dim; c += 32) y[c] = mlr_load(x, c) * mult;
+            for (int c = s.rot_dims + lane; c < s.dim; c += 32) y[c] = act_in(mlr_load(x, c), s.in_act) * mult;
         } else if (s.prep == 2) {
             float sum = 0.0f;
             for (int c = lane; c < s.dim; c += 32) {
-                const float v = mlr_load(x, c);
+                const float v = act_in(mlr_load(x, c), s.in_act);
                 sum = fmaf(v, v, sum);
             }
             const float inv = 1.0f / sqrtf(mlr_warp_sum(sum) + s.unit_eps);
-            for (int c = lane; c < s.dim; c += 32) y[c] = mlr_load(x, c) * inv * mult;
+            for (int c = lane; c < s.dim; c += 32) y[c] = act_in(mlr_load(x, c), s.in_act) * inv * mult;
         } else {
-            for (int c = lane; c < s.dim; c += 32) y[c] = mlr_load(x, c) * mult;
+            for (int c = lane; c < s.dim; c += 32) y[c] = act_in(mlr_load(x, c), s.in_act) * mult;
         }
     }
     if (s.rule == 1) {
@@ -364,7 +374,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan_kernel(const 
 #pragma unroll
         for (int j = 0; j < kVPerThread; ++j) {
             const int i = threadIdx.x + j * kScanWarps * 32;
-            if (i < batch * kScanBlockCols) vs[i] = v_next[j];
+            if (i < batch * kScanBlockCols) vs[i] = act_in(v_next[j], s.in_act);
         }
         if (threadIdx.x < batch) {
             gs[threadIdx.x] = g_next;
@@ -527,7 +537,7 @@ __global__ void __launch_bounds__(kScanWarps * 32) recurrence_scan8_kernel(const
 #pragma unroll
         for (int j = 0; j < kVPerThread; ++j) {
             const int i = threadIdx.x + j * kScanWarps * 32;
-            if (i < batch * kScanBlockCols) vs[i] = mlr_load(&v_next[j], 0);
+            if (i < batch * kScanBlockCols) vs[i] = act_in(mlr_load(&v_next[j], 0), s.in_act);
         }
         if (threadIdx.x < batch) {
             gs[threadIdx.x] = g_next;
@@ -630,10 +640,22 @@ __global__ void __launch_bounds__(128) recurrence_readout_kernel(const float* ob
     mlr_grid_wait();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    __shared__ float scratch[32];
+    float inv_all = 1.0f;
+    if (s.norm_all && s.eps >= 0.0f) {
+        const int total = s.heads * s.vdim;
+        const float* o = obuf + static_cast<size_t>(row) * total;
+        float sum = 0.0f;
+        for (int c = threadIdx.x; c < total; c += blockDim.x) {
+            const float v = __ldcg(o + c);
+            sum = fmaf(v, v, sum);
+        }
+        inv_all = 1.0f / sqrtf(mlr_block_sum(sum, scratch) / static_cast<float>(total) + s.eps);
+    }
     for (int head = warp; head < s.heads; head += warps) {
         const float* o = obuf + (static_cast<size_t>(row) * s.heads + head) * s.vdim;
-        float inv = 1.0f;
-        if (s.eps >= 0.0f) {
+        float inv = inv_all;
+        if (s.eps >= 0.0f && !s.norm_all) {
             float sum = 0.0f;
             for (int c = lane; c < s.vdim; c += 32) {
                 const float v = __ldcg(o + c);
@@ -645,7 +667,7 @@ __global__ void __launch_bounds__(128) recurrence_readout_kernel(const float* ob
         T* orow = out + static_cast<size_t>(row) * ld_out + static_cast<size_t>(head) * s.vdim;
         for (int c = lane; c < s.vdim; c += 32) {
             float value = __ldcg(o + c) * inv;
-            if (s.out_weight) value *= s.out_weight[c];
+            if (s.out_weight) value *= s.out_weight[s.norm_all ? head * s.vdim + c : c];
             if (s.gate_kind) {
                 const float g = mlr_load(grow, s.col_gate + head * s.vdim + c);
                 const float sig = 1.0f / (1.0f + expf(-g));
@@ -704,8 +726,10 @@ __global__ void __launch_bounds__(256) short_conv_state_kernel(const T* in, int 
 }  // namespace
 
 MLR_API int mlr_linear_recurrence(const RecurrenceSpec* spec, const void* proj, int ld, const void* side, int ld_side, int act_bf16, void* out, int ld_out,
-                                  float* state, long long state_stride, const int* segment_info, int n_segments, int* status,
-                                  cudaStream_t stream) {
+                                  float* state, long long state_stride, const int* segment_info, int n_segments, int rows, float* obuf,
+                                  int* status, cudaStream_t stream) {
+    // `obuf` (float32 [rows, heads * vdim], or null): the kernel leaves its plain outputs there and the read-out is a
+    // launch of its own over the step's `rows` rows; a description with norm_all needs it.
     (void)status;
     MLR_REQUIRE(spec, "linear_recurrence: no description");
     const RecurrenceSpec& s = *spec;
@@ -717,6 +741,7 @@ MLR_API int mlr_linear_recurrence(const RecurrenceSpec* spec, const void* proj, 
                 "linear_recurrence: %d rotated values do not fit a head of %d", s.rot_dims, s.dim);
     MLR_REQUIRE(s.rule == 0 ? s.decay != nullptr : (s.rule == 1 && s.a_log && s.dt_bias), "linear_recurrence: the rule's constants are missing");
     MLR_REQUIRE(n_segments >= 0 && state && proj && side && out, "linear_recurrence: bad arguments");
+    MLR_REQUIRE(!s.norm_all || obuf, "linear_recurrence: a norm over all heads needs the buffer of plain outputs");
     if (n_segments == 0) return 0;
     const int cols = s.vdim > 128 ? 8 : 4;
     const int warps = (s.vdim + cols - 1) / cols;
@@ -728,7 +753,7 @@ MLR_API int mlr_linear_recurrence(const RecurrenceSpec* spec, const void* proj, 
     const dim3 grid(n_segments, s.heads);
 #define MLR_GO(T, R, C)                                                                                                     \
     mlr_launch((linear_recurrence_kernel<T, R, C>), dim3(grid), dim3(warps * 32), shared, stream, static_cast<const T*>(proj), ld, static_cast<const T*>(side), ld_side, \
-               static_cast<T*>(out), ld_out, state, state_stride, segment_info, s, batch)
+               static_cast<T*>(out), ld_out, state, state_stride, segment_info, s, batch, obuf)
 #define MLR_PICK(T)                                              \
     do {                                                         \
         if (cols == 4) {                                         \
@@ -746,6 +771,14 @@ MLR_API int mlr_linear_recurrence(const RecurrenceSpec* spec, const void* proj, 
     else MLR_PICK(float);
 #undef MLR_PICK
 #undef MLR_GO
+    if (obuf && rows > 0) {
+        if (act_bf16)
+            mlr_launch((recurrence_readout_kernel<__nv_bfloat16>), dim3(rows), dim3(128), 0, stream, obuf, static_cast<const __nv_bfloat16*>(side),
+                       ld_side, static_cast<__nv_bfloat16*>(out), ld_out, s);
+        else
+            mlr_launch((recurrence_readout_kernel<float>), dim3(rows), dim3(128), 0, stream, obuf, static_cast<const float*>(side), ld_side,
+                       static_cast<float*>(out), ld_out, s);
+    }
     return mlr_launched("linear_recurrence");
 }
 

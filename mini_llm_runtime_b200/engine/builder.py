@@ -136,6 +136,10 @@ class EagerBuilder(_NormHints):
         """The `need` of a launch over `count` rows (nothing to add when the count is a number)."""
         return None
 
+    def bound(self, count: Count) -> int:
+        """The most rows `count` can stand for (a buffer whose size is no multiple of the rows is cut for it)."""
+        return int(count)
+
     # ---- buffers
     def wrap(self, t: Optional[torch.Tensor]) -> Optional[Buf]:
         if t is None:
@@ -274,6 +278,9 @@ class ProgramBuilder(_NormHints):
     def need_for(self, count: Count):
         """The `need` of a launch over `count` rows: one over the wanted rows is skipped when a step wants none."""
         return "want" if isinstance(count, Sym) and count.kind == K_WANT else None
+
+    def bound(self, count: Count) -> int:
+        return self._bound(count)
 
     # ---- buffers
     def _bound(self, rows: Count) -> int:

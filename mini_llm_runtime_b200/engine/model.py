@@ -97,6 +97,7 @@ class Model:
                     self.group_windows.append(need.window)
                 ctx.group = self.group_windows.index(need.window)
             self.runs.append(_RunPlan(block, ctx, need, state_need))
+        self.embedding_state: Optional[torch.Tensor] = None
         self.cache: Optional[CacheManager] = None
         self.cache_config: Optional[CacheConfig] = None
         self.status = None
@@ -172,6 +173,12 @@ class Model:
             if run.state_need is not None:
                 ctx.state = torch.zeros((config.max_requests, *run.state_need.shape), dtype=run.state_need.dtype,
                                         device=self.rt.device)
+        # An embedding may keep a state per request too (what the token before the step's first was).
+        need = self.embedding.state_need() if hasattr(self.embedding, "state_need") else None
+        self.embedding_state = None
+        if need is not None:
+            self.embedding_state = torch.zeros((config.max_requests, *need.shape), dtype=need.dtype, device=self.rt.device)
+            self.embedding.state = self.embedding_state
         for i, run in enumerate(self.runs):
             source = self.plan.schedule[i].kv_from
             if source is not None:
@@ -213,7 +220,7 @@ class Model:
 
     def cache_bytes_per_token(self) -> int:
         element = 2 if self.rt.is_bf16 else 4
-        return sum(r.need.kv_heads * (r.need.head_dim + (r.need.value_dim or r.need.head_dim)) * element for r in self.runs
+        return sum(r.need.kv_heads * (r.need.head_dim + (r.need.head_dim if r.need.value_dim is None else r.need.value_dim)) * element for r in self.runs
                    if r.need is not None and r.context.write_cache)
 
     def _refuse_if_poisoned(self) -> None:
@@ -232,6 +239,8 @@ class Model:
         for run in self.runs:
             if run.context.state is not None:
                 run.context.state[slot].zero_()
+        if self.embedding_state is not None:
+            self.embedding_state[slot].zero_()
         return slot
 
     def close_request(self, slot: int) -> None:
@@ -419,8 +428,10 @@ class Model:
     def _journal_state(self, slots: Sequence[int]):
         """Copies of the fixed-size state of the step's requests, for runs that keep one: a mixer
         updates its state in place, and a step that fails must not leave it half updated."""
-        saved = [(run.context.state, slot, run.context.state[slot].clone())
-                 for run in self.runs if run.context.state is not None for slot in slots]
+        states = [run.context.state for run in self.runs if run.context.state is not None]
+        if self.embedding_state is not None:
+            states.append(self.embedding_state)
+        saved = [(state, slot, state[slot].clone()) for state in states for slot in slots]
         return saved or None
 
     def _restore_state(self, journal) -> None:

@@ -38,6 +38,7 @@ class BuiltParts:
             if block.feed_forward is not None:
                 yield block.feed_forward
             yield from block.norms.values()
+            yield block
         yield self.final_norm
         yield self.lm_head
 
@@ -53,7 +54,8 @@ def build_parts(plan: ModelPlan) -> BuiltParts:
             mixer.position = positions[mixer.position_name]
         feed_forward = build_part("feed_forward", layer.feed_forward) if layer.feed_forward is not None else None
         norms = {slot: build_part("norm", spec) for slot, spec in layer.norms.items()}
-        blocks.append(part_class("block", layer.block)(PartSpec(layer.block), mixer, feed_forward, norms))
+        spec = layer.block if isinstance(layer.block, PartSpec) else PartSpec(layer.block)
+        blocks.append(part_class("block", spec.kind)(spec, mixer, feed_forward, norms))
     return BuiltParts(build_part("embedding", plan.embedding), positions, blocks, build_part("norm", plan.final_norm),
                       build_part("lm_head", plan.lm_head))
 

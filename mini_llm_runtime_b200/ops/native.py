@@ -98,12 +98,34 @@ _SIGNATURES = {
     },
     "recurrence": {
         "mlr_linear_recurrence": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
-                                  c_int, c_void_p, c_void_p],
+                                  c_int, c_int, c_void_p, c_void_p, c_void_p],
         "mlr_linear_recurrence_split": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p,
                                         c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "mlr_short_conv": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
                            c_int, c_void_p],
         "mlr_short_conv_state": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p],
+    },
+    "streams": {
+        "mlr_streams_step": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                             c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlr_embed_hashed": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
+                             c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+    },
+    "latent": {
+        "mlr_latent_cache": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_void_p, c_void_p],
+        "mlr_head_project": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "experts": {
+        "mlr_experts_route": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "mlr_experts_arrange": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p],
+        "mlr_experts_max_tiles": [c_int, c_int],
+        "mlr_experts_product": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "mlr_experts_combine": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                                c_longlong, c_int, c_int, c_void_p],
     },
     "weights": {
         "mlr_normal_fill": [c_void_p, c_int, c_longlong, c_ulonglong, c_double, c_int, c_void_p],

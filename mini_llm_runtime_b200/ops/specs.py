@@ -16,19 +16,20 @@ class MaskedAttentionSpec(ctypes.Structure):
     _fields_ = [("freq", ctypes.c_void_p),
                 ("heads", ctypes.c_int32), ("kv_heads", ctypes.c_int32), ("dim", ctypes.c_int32), ("vdim", ctypes.c_int32),
                 ("rot_dims", ctypes.c_int32), ("window", ctypes.c_int32), ("chunk", ctypes.c_int32), ("sink", ctypes.c_int32),
-                ("gate_kind", ctypes.c_int32),
+                ("gate_kind", ctypes.c_int32), ("shared_kv", ctypes.c_int32),
                 ("scale", ctypes.c_float), ("out_scale", ctypes.c_float)]
 
 
 class RecurrenceSpec(ctypes.Structure):
     PREP = {None: 0, "rotate": 1, "unit": 2}
     RULE = {"decay": 0, "delta": 1}
+    IN_ACT = {None: 0, "silu": 1}
     _fields_ = [("freq", ctypes.c_void_p), ("decay", ctypes.c_void_p), ("a_log", ctypes.c_void_p), ("dt_bias", ctypes.c_void_p),
                 ("out_weight", ctypes.c_void_p),
                 ("heads", ctypes.c_int32), ("qk_heads", ctypes.c_int32), ("dim", ctypes.c_int32), ("vdim", ctypes.c_int32),
                 ("prep", ctypes.c_int32), ("rot_dims", ctypes.c_int32), ("rule", ctypes.c_int32), ("gate_kind", ctypes.c_int32),
                 ("col_q", ctypes.c_int32), ("col_k", ctypes.c_int32), ("col_v", ctypes.c_int32), ("col_a", ctypes.c_int32),
-                ("col_b", ctypes.c_int32), ("col_gate", ctypes.c_int32),
+                ("col_b", ctypes.c_int32), ("col_gate", ctypes.c_int32), ("in_act", ctypes.c_int32), ("norm_all", ctypes.c_int32),
                 ("q_mult", ctypes.c_float), ("k_mult", ctypes.c_float), ("unit_eps", ctypes.c_float), ("eps", ctypes.c_float),
                 ("out_scale", ctypes.c_float)]
 

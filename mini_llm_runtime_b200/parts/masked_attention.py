@@ -94,32 +94,41 @@ class MaskedAttentionMixer(SequenceCore):
             b.launch("attention_masked", "mlr_kv_rope_cache", address(self.desc), k.ptr, k.ld, v.ptr, v.ld, proj.is_bf16,
                      run.cache.data_ptr(), run.cache.shape[0], b.meta("positions"), b.meta("segment_of_row"), table, stride,
                      b.page_size, proj.rows, b.status, b.stream)
-        args = (address(self.desc), proj.ptr, proj.ld, gate.ptr if gate else None, gate.ld if gate else 0, act.ptr, act.ld)
-        where = (run.cache.data_ptr(), run.cache.shape[0])
-        tiled = (proj.dtype is torch.bfloat16 and native.module("attention_masked").mlr_attention_masked_tiles_fit(self.dim, self.vdim)
-                 and act.ld % 2 == 0 and act.ptr % 4 == 0)
-        if not tiled:
-            # One block per (row, head): the float32 path, and sizes the tiled kernel does not take.
-            b.launch("attention_masked", "mlr_attention_masked", *args, proj.is_bf16, *where, b.meta("positions"),
-                     b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, 0, 1, 1, None, b.status, b.stream)
-            return
-        # The step's launch plan (made by the native executor from the step's segments, shared by all layers):
-        # segments of few rows (a decoded token, a short portion) go to the row kernel, prompt portions in tiles of 64
-        # rows to the tensor-core kernel.
-        # The row kernel cuts long contexts into key ranges that run as blocks of their own (the plan's split of the keys and
-        # its scratch for the ranges' partial results: 16 rows x kv heads x splits x (head size + 2) floats per segment).
-        # The planner sizes the scratch by the head size it is told: FINER times the room of a range's (value size + 2)
-        # floats lets the kernel cut every planned range into FINER (its blocks wait for memory most of the time, and
-        # more of them in flight is what makes a long context fast; the planner's own split is tuned for a kernel that
-        # copies keys in bulk).
-        group = self.heads // self.kv_heads
-        plan = b.plan((group if group <= 16 else 1, self.kv_heads, 0, 0, self.FINER * (max(self.dim, self.vdim) + 2), 1))
-        info = b.meta("segment_info")
-        split = (plan.chunk, plan.max_splits, self.FINER, plan.scratch) if group <= 16 else (0, 1, 1, None)
-        b.launch("attention_masked", "mlr_attention_masked", *args, 1, *where, b.meta("positions"), b.meta("segment_of_row"), table,
-                 stride, b.page_size, 0, plan.items, plan.n_items, info, *split, b.status, b.stream, need=plan.n_items)
-        b.launch("attention_masked", "mlr_attention_masked_tiles", *args, *where, plan.tiles, plan.n_tiles, info, table, stride,
-                 b.page_size, b.status, b.stream, need=plan.n_tiles)
+        emit_masked_attention(b, self.desc, proj, gate, act, run, self.FINER)
+
+
+def emit_masked_attention(b, desc: MaskedAttentionSpec, q, gate, act, run: RunContext, finer: int = 4) -> None:
+    """The attention launches of a step for the description `desc`: queries from `q` (head h at column h * dim), the gate's
+    columns or None, the result into `act`, keys and values from the run's cache."""
+    heads, kv_heads, dim, vdim = desc.heads, desc.kv_heads, desc.dim, desc.vdim
+    proj = q
+    table, stride = b.table(run.group), b.table_stride(run.group)
+    args = (address(desc), proj.ptr, proj.ld, gate.ptr if gate else None, gate.ld if gate else 0, act.ptr, act.ld)
+    where = (run.cache.data_ptr(), run.cache.shape[0])
+    tiled = (proj.dtype is torch.bfloat16 and native.module("attention_masked").mlr_attention_masked_tiles_fit(dim, vdim)
+             and act.ld % 2 == 0 and act.ptr % 4 == 0)
+    if not tiled:
+        # One block per (row, head): the float32 path, and sizes the tiled kernel does not take.
+        b.launch("attention_masked", "mlr_attention_masked", *args, proj.is_bf16, *where, b.meta("positions"),
+                 b.meta("segment_of_row"), table, stride, b.page_size, proj.rows, None, 0, None, 0, 1, 1, None, b.status, b.stream)
+        return
+    # The step's launch plan (made by the native executor from the step's segments, shared by all layers):
+    # segments of few rows (a decoded token, a short portion) go to the row kernel, prompt portions in tiles of 64
+    # rows to the tensor-core kernel.
+    # The row kernel cuts long contexts into key ranges that run as blocks of their own (the plan's split of the keys and
+    # its scratch for the ranges' partial results: 16 rows x kv heads x splits x (head size + 2) floats per segment).
+    # The planner sizes the scratch by the head size it is told: FINER times the room of a range's (value size + 2)
+    # floats lets the kernel cut every planned range into FINER (its blocks wait for memory most of the time, and
+    # more of them in flight is what makes a long context fast; the planner's own split is tuned for a kernel that
+    # copies keys in bulk).
+    group = heads // kv_heads
+    plan = b.plan((group if group <= 16 else 1, kv_heads, 0, 0, finer * (max(dim, vdim) + 2), 1))
+    info = b.meta("segment_info")
+    split = (plan.chunk, plan.max_splits, finer, plan.scratch) if group <= 16 else (0, 1, 1, None)
+    b.launch("attention_masked", "mlr_attention_masked", *args, 1, *where, b.meta("positions"), b.meta("segment_of_row"), table,
+             stride, b.page_size, 0, plan.items, plan.n_items, info, *split, b.status, b.stream, need=plan.n_items)
+    b.launch("attention_masked", "mlr_attention_masked_tiles", *args, *where, plan.tiles, plan.n_tiles, info, table, stride,
+             b.page_size, b.status, b.stream, need=plan.n_tiles)
 
 
 register_part("mixer", "masked_attention", MaskedAttentionMixer)

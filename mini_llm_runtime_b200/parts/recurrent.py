@@ -31,11 +31,15 @@ def emit_recurrence(b, mixer, proj, side, act, run: RunContext) -> None:
     """The recurrence of `mixer.desc` over the step's rows: q, k, v from `proj`, the rule's inputs and the gate
     from `side`, the result into `act`.  Few rows: one kernel.  Many: prepare, scan, read-out."""
     state, info = run.state, b.meta("segment_info")
-    if b.le(proj.rows, b.rt.recurrence_fused_rows):
-        b.launch("recurrence", "mlr_linear_recurrence", address(mixer.desc), proj.ptr, proj.ld, side.ptr, side.ld, proj.is_bf16,
-                 act.ptr, act.ld, state.data_ptr(), state.stride(0), info, b.segments, b.status, b.stream)
-        return
     d = mixer.desc
+    if b.le(proj.rows, b.rt.recurrence_fused_rows):
+        # A read-out that norms all heads of a token together cannot happen in a block that owns one head: the kernel then
+        # leaves its plain float32 outputs in a buffer and the read-out is a second launch.
+        plain = b.temp(proj.rows, d.heads * d.vdim, torch.float32) if d.norm_all else None
+        b.launch("recurrence", "mlr_linear_recurrence", address(d), proj.ptr, proj.ld, side.ptr, side.ld, proj.is_bf16,
+                 act.ptr, act.ld, state.data_ptr(), state.stride(0), info, b.segments, proj.rows, plain.ptr if plain else None,
+                 b.status, b.stream)
+        return
     qf = b.temp(proj.rows, d.qk_heads * d.dim, torch.float32)
     kf = b.temp(proj.rows, d.qk_heads * d.dim, torch.float32)
     gates = b.temp(proj.rows, 2 * d.heads, torch.float32)
@@ -182,3 +186,56 @@ class DeltaRuleMixer(SequenceCore):
 
 register_part("mixer", "retention", RetentionMixer)
 register_part("mixer", "delta_rule", DeltaRuleMixer)
+
+
+class LightningMixer(SequenceCore):
+    """Lightning attention: linear attention with a fixed decay per head, no positions and no scale.
+
+        q, k = silu(Wq x), silu(Wk x) [H, D];  v = silu(Wv x) [H, Dv];  S <- decay_h S + k v^T;  o = S^T q;
+        all heads of a token together over their root mean square, times a weight [H Dv], times sigmoid(Wg x);  result = o Wo^T.
+
+    Parameters: hidden_size, num_heads, head_dim, value_dim, decay (one per head), eps.  Weights: "q", "k" [H D, W],
+    "v", "g" [H Dv, W], "o" [W, H Dv], "norm" [H Dv].  The state is the retention mixer's: float32 [H, Dv, D] per request."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = spec.params
+        self.width = int(p["hidden_size"])
+        self.heads, self.dim, self.vdim = int(p["num_heads"]), int(p["head_dim"]), int(p["value_dim"])
+        self.decay = [float(d) for d in p["decay"]]
+        self.eps = float(p["eps"])
+        if len(self.decay) != self.heads:
+            raise ConfigError(f"{len(self.decay)} decays for {self.heads} heads")
+        _check_state_size(self.dim, self.vdim)
+        self.desc: Optional[RecurrenceSpec] = None
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.heads * self.vdim * self.dim,), torch.float32)
+
+    def in_roles(self) -> List[Tuple[str, int]]:
+        return [("q", self.heads * self.dim), ("k", self.heads * self.dim), ("v", self.heads * self.vdim), ("g", self.heads * self.vdim)]
+
+    def core_width(self) -> int:
+        return self.heads * self.vdim
+
+    def extra_weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.spec.weights["norm"], (self.heads * self.vdim,), "vector", ("one_plus_normal", 0.01))]
+
+    def kernel_modules(self, dtype) -> List[str]:
+        return ["recurrence"] + F.product_modules(dtype)
+
+    def bind_core(self, tensors, rt, out_scale: float) -> None:
+        at = self.in_columns()
+        self._held = (torch.tensor(self.decay, dtype=torch.float32, device=rt.device),
+                      rt.vector(tensors[self.spec.weights["norm"]]).float().contiguous())
+        self.desc = RecurrenceSpec(
+            decay=self._held[0].data_ptr(), out_weight=self._held[1].data_ptr(), heads=self.heads, qk_heads=self.heads, dim=self.dim,
+            vdim=self.vdim, prep=RecurrenceSpec.PREP[None], rot_dims=0, rule=RecurrenceSpec.RULE["decay"], gate_kind=GATES["sigmoid"],
+            col_q=at["q"], col_k=at["k"], col_v=at["v"], col_gate=at["g"], in_act=RecurrenceSpec.IN_ACT["silu"], norm_all=1,
+            q_mult=1.0, k_mult=1.0, unit_eps=0.0, eps=self.eps, out_scale=float(out_scale))
+
+    def emit_core(self, b, proj, act, run: RunContext) -> None:
+        emit_recurrence(b, self, proj, proj, act, run)
+
+
+register_part("mixer", "lightning", LightningMixer)

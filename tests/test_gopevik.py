@@ -364,7 +364,7 @@ def _recurrence_case(dtype, rule, heads, qk_heads, dim, vdim, rot_dims, segments
         else:
             _call("recurrence", "mlr_linear_recurrence", ctypes.addressof(spec), proj.data_ptr(), proj.stride(0), proj.data_ptr(),
                   proj.stride(0), native.is_bf16(proj), out.data_ptr(), out.stride(0), state.data_ptr(), state.stride(0),
-                  seg_info.data_ptr(), len(segments), None, native.stream())
+                  seg_info.data_ptr(), len(segments), 0, None, None, native.stream())
         for i, (f, c, _, _) in enumerate(info):
             got[i].append(out[f:f + c].float().cpu().double())
     wants = []
