@@ -301,6 +301,30 @@ def gopevik_config(width, ff, heads, kv, dim, layers, chunk, vocab):
             "layers": [(side, side, delta, side)[i % 4] for i in range(layers)]}
 
 
+def niridra_config(width, ff, heads, kv, dim, layers, chunk, vocab):
+    """Latent attention (a cached vector of `dim` values per token), lightning attention, latent attention, and latent
+    attention that shares the cache of the layer before it; four copies of the stream; every layer with sixteen routed experts
+    of ff / 6 of which four are used beside a shared one of ff / 3, so that a token multiplies as many feed-forward weights as
+    in the dense layer (the layer holds 3 x as many)."""
+    mlp = {"kind": "moe", "expert": {"ff": ff // 6}, "shared": {"ff": ff // 3},
+           "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    latent = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": dim, "scale": dim ** -0.5}
+    lightning = {"heads": heads, "dim": dim, "vdim": dim, "decay": [1 - 2.0 ** (-5 - i % 4) for i in range(heads)]}
+    made = []
+    for i in range(layers):
+        if i % 4 == 1:
+            made.append({"type": "lightning", "mixer": lightning, "mlp": mlp})
+        elif i % 4 == 3:
+            made.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 1), "mlp": mlp})
+        else:
+            made.append({"type": "latent_attention", "mixer": latent, "mlp": mlp})
+    return {"architecture": "Niridra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 4,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": made}
+
+
+DESIGNS = {"gopevik": gopevik_config, "niridra": niridra_config}
+
+
 def compare_designs(args) -> int:
     """Prefill (one request of `--context` tokens in one step) and decode (`--batch` requests at that context, one token
     each a step, replayed from CUDA graphs) of both designs, `--layers` layers each (default 4), timed with CUDA events
@@ -360,12 +384,15 @@ def compare_designs(args) -> int:
         for name, width, ff, heads, kv, dim in COMPARE_SIZES:
             qwen = dict(QWEN3_8B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv,
                         head_dim=dim, intermediate_size=ff, vocab_size=vocab)
-            g = measure(gopevik_config(width, ff, heads, kv, dim, layers, context, vocab))
+            g = measure(DESIGNS[args.compare](width, ff, heads, kv, dim, layers, context, vocab))
             q = measure(qwen)
-            results[name] = {"gopevik": g, "qwen3": q,
+            results[name] = {args.compare: g, "qwen3": q,
                              "prefill_ratio": g["prefill_tokens_per_s"] / q["prefill_tokens_per_s"],
                              "decode_ratio": g["decode_tokens_per_s"] / q["decode_tokens_per_s"]}
-    print(json.dumps({"metric": "prefill and decode tok/s of the Gopevik design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
+            if args.compare != "gopevik":       # the other hybrid design of the package, as a second neighbour
+                other = measure(gopevik_config(width, ff, heads, kv, dim, layers, context, vocab))
+                results[name]["gopevik"] = other
+    print(json.dumps({"metric": f"prefill and decode tok/s of the {args.compare.capitalize()} design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
                       "layers": layers, "context": context, "batch": batch, "steps": steps, "warmup": warmup, "dtype": "bf16",
                       "data": "synthetic", "sizes": results, "clocks": clocks.summary()}))
     return 0
@@ -391,7 +418,7 @@ def main() -> int:
                     help="every matrix product on the package's tcgen05 kernel, none on the vendor library (slower)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the baseline's configuration has 16; 64 is a little faster)")
     ap.add_argument("--no-check", action="store_true", help="skip the agreement check of bfloat16 and float32 before the measurement")
-    ap.add_argument("--compare", default=None, choices=["gopevik"],
+    ap.add_argument("--compare", default=None, choices=sorted(DESIGNS),
                     help="instead of the headline: prefill and decode of the named design beside Qwen3 at equal layer sizes "
                          "(--layers layers, default 4; --context, default 2048; --batch); prints one JSON line of its own")
     args = ap.parse_args()

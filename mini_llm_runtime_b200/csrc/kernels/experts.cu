@@ -206,6 +206,117 @@ __global__ void __launch_bounds__(256) expert_product_kernel(const T* a, long lo
     }
 }
 
+// ---- the same product on the tensor cores (bfloat16 operands, float32 sums) ----
+// A block owns the tile's 32 rows x 128 columns: 8 warps as 2 x 4, a warp 16 rows x 32 columns (four n8 pieces, and as many
+// again for the second matrix when DUAL).  Rows of A (gathered) and of W arrive 32 values of K at a time by asynchronous
+// 16-byte copies into one of two stages while the other is multiplied; fragments by ldmatrix from rows padded to 80 bytes.
+// A sum runs over K in the order of the instruction's own tree within 16 values and k = 0, 16, 32 .. between them, whatever
+// else is in the tile.
+constexpr int kMmaCols = 128, kMmaK = 32, kMmaLd = 40;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+template <typename TO, bool DUAL>
+__global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bfloat16* a, long long lda, const int* source, int divisor,
+                                                                 const __nv_bfloat16* w, const __nv_bfloat16* w2, int N, int K, TO* out,
+                                                                 long long ldo, const int* tiles, const int* n_tiles) {
+    mlr_grid_wait();
+    const int tile = blockIdx.y;
+    if (tile >= __ldcg(n_tiles)) return;
+    const int expert = __ldcg(tiles + 3 * tile), row0 = __ldcg(tiles + 3 * tile + 1), rows = __ldcg(tiles + 3 * tile + 2);
+    const int col0 = blockIdx.x * kMmaCols;
+    __shared__ __align__(16) __nv_bfloat16 As[2][kTileRows * kMmaLd];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][kMmaCols * kMmaLd];
+    __shared__ __align__(16) __nv_bfloat16 W2s[2][DUAL ? kMmaCols * kMmaLd : 8];
+    __shared__ long long arow[kTileRows];
+    if (threadIdx.x < kTileRows) {
+        const int r = row0 + min(static_cast<int>(threadIdx.x), rows - 1);
+        arow[threadIdx.x] = static_cast<long long>(source ? __ldcg(source + r) / divisor : r) * lda;
+    }
+    __syncthreads();
+    const __nv_bfloat16* we = w + static_cast<size_t>(expert) * N * K;
+    const __nv_bfloat16* we2 = DUAL ? w2 + static_cast<size_t>(expert) * N * K : nullptr;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wm = warp >> 2, wn = warp & 3;                 // the warp's 16 rows and 32 columns
+    auto fetch = [&](int k0, int stage) {
+        if (threadIdx.x < kTileRows * 4) {
+            const int r = threadIdx.x >> 2, k = k0 + (threadIdx.x & 3) * 8;
+            mlr_async_copy16(&As[stage][r * kMmaLd + (threadIdx.x & 3) * 8], k < K ? a + arow[r] + k : a, k < K);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int i = threadIdx.x + 256 * j;
+            const int n = i >> 2, k = k0 + (i & 3) * 8;
+            const bool real = col0 + n < N && k < K;
+            const size_t at = static_cast<size_t>(col0 + n) * K + k;
+            mlr_async_copy16(&Ws[stage][n * kMmaLd + (i & 3) * 8], real ? we + at : we, real);
+            if (DUAL) mlr_async_copy16(&W2s[stage][n * kMmaLd + (i & 3) * 8], real ? we2 + at : we2, real);
+        }
+        mlr_async_commit();
+    };
+    float acc[4][4] = {}, acc2[DUAL ? 4 : 1][4] = {};
+    const int steps = (K + kMmaK - 1) / kMmaK;
+    fetch(0, 0);
+    // ldmatrix addresses of this lane: A rows (lane & 15) at k (lane >> 4) * 8; W rows n = (lane & 7) + (lane >> 4) * 8 at k ((lane >> 3) & 1) * 8.
+    const int a_off = (wm * 16 + (lane & 15)) * kMmaLd + (lane >> 4) * 8;
+    const int b_off = (wn * 32 + (lane & 7) + (lane >> 4) * 8) * kMmaLd + ((lane >> 3) & 1) * 8;
+    for (int step = 0; step < steps; ++step) {
+        const int stage = step & 1;
+        if (step + 1 < steps) {
+            fetch((step + 1) * kMmaK, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            mlr_async_wait();
+        }
+        __syncthreads();
+        const uint32_t a_base = static_cast<uint32_t>(__cvta_generic_to_shared(&As[stage][0]));
+        const uint32_t b_base = static_cast<uint32_t>(__cvta_generic_to_shared(&Ws[stage][0]));
+        const uint32_t b2_base = static_cast<uint32_t>(__cvta_generic_to_shared(&W2s[stage][0]));
+#pragma unroll
+        for (int ks = 0; ks < kMmaK / 16; ++ks) {
+            uint32_t fa[4];
+            ldmatrix_x4(fa, a_base + 2 * (a_off + ks * 16));
+#pragma unroll
+            for (int pair = 0; pair < 2; ++pair) {
+                uint32_t fb[4];
+                ldmatrix_x4(fb, b_base + 2 * (b_off + pair * 16 * kMmaLd + ks * 16));
+                mma_bf16(acc[2 * pair], fa, fb[0], fb[1]);
+                mma_bf16(acc[2 * pair + 1], fa, fb[2], fb[3]);
+                if (DUAL) {
+                    ldmatrix_x4(fb, b2_base + 2 * (b_off + pair * 16 * kMmaLd + ks * 16));
+                    mma_bf16(acc2[2 * pair], fa, fb[0], fb[1]);
+                    mma_bf16(acc2[2 * pair + 1], fa, fb[2], fb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    mlr_grid_dependents_may_start();
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * 16 + (lane >> 2) + 8 * half;
+            const int c = col0 + wn * 32 + piece * 8 + (lane & 3) * 2;
+            if (r >= rows) continue;
+            TO* orow = out + static_cast<size_t>(row0 + r) * ldo;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (c + j >= N) continue;
+                float value = acc[piece][2 * half + j];
+                if (DUAL) value = value / (1.0f + expf(-value)) * acc2[piece][2 * half + j];
+                mlr_store(orow, c + j, value);
+            }
+        }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) combine_kernel(const float* y, long long ldy, const int* row_of_pair, const float* weights, int top,
                                                       const T* shared_y, long long ld_shared, const float* shared_gate, float* out,
@@ -266,6 +377,15 @@ MLR_API int mlr_experts_arrange(int* counts, const int* chosen, const int* place
     return mlr_launched("experts_arrange");
 }
 
+// MLR_EXPERTS_SIMT=1 keeps the bfloat16 products on the CUDA cores (for comparing the two kernels).
+static bool mlr_experts_simt_only() {
+    static const bool only = [] {
+        const char* v = getenv("MLR_EXPERTS_SIMT");
+        return v && v[0] == '1';
+    }();
+    return only;
+}
+
 // The most tiles `pairs` rows of `experts` experts can make (the size of the grid, and of `tiles` / 3).
 MLR_API int mlr_experts_max_tiles(int pairs, int experts) { return pairs / kTileRows + experts; }
 
@@ -281,6 +401,22 @@ MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, cons
     const int max_tiles = mlr_experts_max_tiles(pairs, experts);
     MLR_REQUIRE(max_tiles <= 65535, "experts_product: %d row tiles are more than a grid takes", max_tiles);
     const dim3 grid((N + kTileCols - 1) / kTileCols, max_tiles);
+    // bfloat16 rows that start on 16-byte borders go to the tensor cores.
+    if (act_bf16 && K % 8 == 0 && lda % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+        (!gated || reinterpret_cast<uintptr_t>(w2) % 16 == 0) && !mlr_experts_simt_only()) {
+        const dim3 wide((N + kMmaCols - 1) / kMmaCols, max_tiles);
+        const __nv_bfloat16 *ab = static_cast<const __nv_bfloat16*>(a), *wb = static_cast<const __nv_bfloat16*>(w),
+                            *w2b = static_cast<const __nv_bfloat16*>(w2);
+        if (gated && !out_f32)
+            mlr_launch((expert_product_mma_kernel<__nv_bfloat16, true>), dim3(wide), dim3(256), 0, stream, ab, lda, source, divisor, wb, w2b, N, K,
+                       static_cast<__nv_bfloat16*>(out), ldo, tiles, n_tiles);
+        else if (!gated && out_f32)
+            mlr_launch((expert_product_mma_kernel<float, false>), dim3(wide), dim3(256), 0, stream, ab, lda, source, divisor, wb, w2b, N, K,
+                       static_cast<float*>(out), ldo, tiles, n_tiles);
+        else
+            return mlr_fail("experts_product: this pair of precisions is not built");
+        return mlr_launched("experts_product");
+    }
 #define MLR_GO(T, TO, DUAL)                                                                                                              \
     mlr_launch((expert_product_kernel<T, TO, DUAL>), dim3(grid), dim3(256), 0, stream, static_cast<const T*>(a), lda, source, divisor,   \
                static_cast<const T*>(w), static_cast<const T*>(w2), N, K, static_cast<TO*>(out), ldo, tiles, n_tiles)

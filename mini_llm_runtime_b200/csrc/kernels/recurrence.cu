@@ -52,6 +52,11 @@ namespace {
 
 __device__ __forceinline__ float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float act_in(float x, int kind) { return kind == 1 ? x / (1.0f + expf(-x)) : x; }
+// The turn of a pair by an angle, with its roundings spelled out: the one-kernel form and the prepare kernel give the same bits.
+__device__ __forceinline__ void turn(float u, float v, float cs, float sn, float& a, float& b) {
+    a = __fmaf_rn(u, cs, -__fmul_rn(v, sn));
+    b = __fmaf_rn(v, cs, __fmul_rn(u, sn));
+}
 
 template <typename T, int R, int COLS>
 __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, int ld, const T* side, int ld_side, T* out, int ld_out, float* state,
@@ -112,18 +117,14 @@ __global__ void __launch_bounds__(1024) linear_recurrence_kernel(const T* proj, 
                 float sn, cs;
                 sincosf(static_cast<float>(start + base + t) * s.freq[c], &sn, &cs);
                 float* x = qs + static_cast<size_t>(t) * s.dim;
-                float u = x[c], v = x[c + half];
-                x[c] = u * cs - v * sn;
-                x[c + half] = v * cs + u * sn;
+                turn(x[c], x[c + half], cs, sn, x[c], x[c + half]);
                 x = ks + static_cast<size_t>(t) * s.dim;
-                u = x[c], v = x[c + half];
-                x[c] = u * cs - v * sn;
-                x[c + half] = v * cs + u * sn;
+                turn(x[c], x[c + half], cs, sn, x[c], x[c + half]);
             }
             __syncthreads();
             for (int i = threadIdx.x; i < n * s.dim; i += threads) {
-                qs[i] *= s.q_mult;
-                ks[i] *= s.k_mult;
+                qs[i] = __fmul_rn(qs[i], s.q_mult);
+                ks[i] = __fmul_rn(ks[i], s.k_mult);
             }
         } else if (s.prep == 2) {
             for (int vec = warp; vec < 2 * n; vec += warps) {
@@ -268,8 +269,10 @@ __global__ void __launch_bounds__(128) recurrence_prepare_kernel(const T* proj, 
                 float sn, cs;
                 sincosf(position * s.freq[c], &sn, &cs);
                 const float u = act_in(mlr_load(x, c), s.in_act), v = act_in(mlr_load(x, c + half), s.in_act);
-                y[c] = (u * cs - v * sn) * mult;
-                y[c + half] = (v * cs + u * sn) * mult;
+                float a, b;
+                turn(u, v, cs, sn, a, b);
+                y[c] = __fmul_rn(a, mult);
+                y[c + half] = __fmul_rn(b, mult);
             }
             for (int c = s.rot_dims + lane; c < s.dim; c += 32) y[c] = act_in(mlr_load(x, c), s.in_act) * mult;
         } else if (s.prep == 2) {

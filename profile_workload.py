@@ -5,7 +5,7 @@ Qwen3-8B layer sizes with few layers, bracketed by cudaProfilerStart/Stop.
     python profile_workload.py prefill [--layers 2] [--tokens 2048] [--mma-sync-attention]
     python profile_workload.py attention [--page-size 64]
     python profile_workload.py products  [--tokens 2048]
-    python profile_workload.py decode|prefill --design gopevik [--layers 4] [--context 2048]
+    python profile_workload.py decode|prefill --design gopevik|niridra [--layers 4] [--context 2048]
 
 `attention` times the two bfloat16 attention kernels alone (CUDA events, no model) over a
 range of prompt lengths, contexts, batch sizes and head sizes and prints two tables.
@@ -60,8 +60,8 @@ def main() -> int:
                     help="up to how many rows a product takes the CUDA-core pass over the weights (default: the runtime's setting)")
     ap.add_argument("--mma-sync-attention", action="store_true",
                     help="prompt attention on the mma.sync kernel instead of the tcgen05 one")
-    ap.add_argument("--design", default="qwen3", choices=["qwen3", "gopevik"],
-                    help="gopevik: the hybrid design at the layer sizes of `bench.py --compare gopevik` (width 2048; decode and prefill)")
+    ap.add_argument("--design", default="qwen3", choices=["qwen3", "gopevik", "niridra"],
+                    help="gopevik, niridra: the design at the layer sizes of `bench.py --compare <design>` (width 2048; decode and prefill)")
     args = ap.parse_args()
 
     if args.mode == "attention":
@@ -76,10 +76,10 @@ def main() -> int:
 
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     length = args.context if args.mode == "decode" else args.tokens
-    if args.design == "gopevik":
-        from bench import COMPARE_SIZES, gopevik_config
+    if args.design != "qwen3":
+        from bench import COMPARE_SIZES, DESIGNS
         _, width, ff, heads, kv, dim = COMPARE_SIZES[0]
-        cfg = gopevik_config(width, ff, heads, kv, dim, args.layers, max(length + 64, 2048), 32000)
+        cfg = DESIGNS[args.design](width, ff, heads, kv, dim, args.layers, max(length + 64, 2048), 32000)
         cfg["vocab_size"] = cfg["vocab"]
     batch = args.batch if args.mode == "decode" else 1
     model = random_model(cfg, 2, "bfloat16", CacheConfig(page_size=args.page_size, num_pages=batch * (length // args.page_size + 8),

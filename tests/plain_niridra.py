@@ -121,7 +121,8 @@ def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, top
 
 def experts_feed_forward(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
     r = mlp["router"]
-    chosen, weights = route(h, w[p + "router"], w[p + "correction"], r["top"], r["groups"]["count"], r["groups"]["keep"])
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    chosen, weights = route(h, w[p + "router"], w[p + "correction"], r["top"], groups["count"], groups["keep"])
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for j in range(chosen.shape[1]):
