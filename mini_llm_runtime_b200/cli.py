@@ -161,13 +161,16 @@ def inspect(model_dir: str) -> dict:
         raw = json.load(f)
     keys = ("hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim",
             "intermediate_size", "vocab_size", "max_position_embeddings", "rms_norm_eps", "rope_theta",
-            "tie_word_embeddings", "use_sliding_window", "sliding_window", "max_window_layers", "width", "vocab", "norm")
+            "tie_word_embeddings", "use_sliding_window", "sliding_window", "max_window_layers", "width", "vocab", "norm", "streams",
+            "embedding")
     windows = sorted({str(layer.mixer.params.get("window")) for layer in plan.layers})
     return {"container": "safetensors", "files": len(files), "bytes": sum(os.path.getsize(f.path) for f in files),
             "tensors": len(stored), "stored_dtypes": dtypes,
             "architecture": plan.architecture, "dimensions": {k: raw[k] for k in keys if k in raw},
             "layers": len(plan.layers), "runs": len(plan.schedule), "windows": windows,
             "mixers": [layer.mixer.kind for layer in plan.layers],
+            "feed_forwards": [layer.feed_forward.kind if layer.feed_forward is not None else None for layer in plan.layers],
+            "cache_from": [run.kv_from for run in plan.schedule],
             "missing_tensors": sorted(expected - set(stored)), "unexpected_tensors": sorted(set(stored) - expected - redundant)}
 
 

@@ -17,7 +17,7 @@
 
 namespace {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 constexpr int kThreads = 256;
 
 struct StreamWeights {

@@ -24,7 +24,7 @@ from ..ops import native
 from ..weights.loader import WeightSpec
 from .base import Block, Embedding, Norm, StateNeed
 
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 class HashedEmbedding(Embedding):
