@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int kRouteThreads = 128;
+constexpr int kRouteThreads = 256;
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxTop = 32;
 constexpr int kTileRows = 32;     // rows of one expert per block of a product
@@ -44,7 +44,20 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
     for (int e = warp; e < experts + has_gate; e += warps) {
         const float* w = router + static_cast<size_t>(e) * width;
         float sum = 0.0f;
-        for (int c = lane; c < width; c += 32) sum = fmaf(w[c], xs[c], sum);
+        if (width % 4 == 0) {         // 16 bytes at a time (rows of the router and the shared row start on 16-byte borders then)
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* x4 = reinterpret_cast<const float4*>(xs);
+#pragma unroll 4
+            for (int c = lane; c < width / 4; c += 32) {
+                const float4 a = w4[c], b = x4[c];
+                sum = fmaf(a.x, b.x, sum);
+                sum = fmaf(a.y, b.y, sum);
+                sum = fmaf(a.z, b.z, sum);
+                sum = fmaf(a.w, b.w, sum);
+            }
+        } else {
+            for (int c = lane; c < width; c += 32) sum = fmaf(w[c], xs[c], sum);
+        }
         sum = mlr_warp_sum(sum);
         if (lane == 0) {
             const float s = 1.0f / (1.0f + expf(-sum));
@@ -101,7 +114,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
 
 // One block.  first_row [experts + 1]; tiles: {expert, first row, rows} per tile, n_tiles[0] their number; row_of_pair [pairs]
 // (the row of pair = token * top + choice in the order by expert), pair_of_row [pairs] the other way.
-__global__ void __launch_bounds__(1024) arrange_kernel(int* counts, const int* chosen, const int* place, int experts, int pairs,
+__global__ void __launch_bounds__(1024) arrange_kernel(int* counts, const int* chosen, const int* place, int experts, int pairs, int tile_rows,
                                                        int* first_row, int* tiles, int* n_tiles, int* row_of_pair, int* pair_of_row) {
     mlr_grid_wait();
     __shared__ int first[kMaxExperts + 1];
@@ -112,7 +125,7 @@ __global__ void __launch_bounds__(1024) arrange_kernel(int* counts, const int* c
             first[e] = rows;
             first_tile[e] = t;
             rows += counts[e];
-            t += (counts[e] + kTileRows - 1) / kTileRows;
+            t += (counts[e] + tile_rows - 1) / tile_rows;
         }
         first[experts] = rows;
         first_tile[experts] = t;
@@ -122,10 +135,10 @@ __global__ void __launch_bounds__(1024) arrange_kernel(int* counts, const int* c
     for (int e = threadIdx.x; e <= experts; e += blockDim.x) first_row[e] = first[e];
     for (int e = threadIdx.x; e < experts; e += blockDim.x) {
         const int n = first[e + 1] - first[e];
-        for (int t = first_tile[e], r = 0; r < n; ++t, r += kTileRows) {
+        for (int t = first_tile[e], r = 0; r < n; ++t, r += tile_rows) {
             tiles[3 * t] = e;
             tiles[3 * t + 1] = first[e] + r;
-            tiles[3 * t + 2] = min(kTileRows, n - r);
+            tiles[3 * t + 2] = min(tile_rows, n - r);
         }
         counts[e] = 0;
     }
@@ -223,7 +236,11 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) 
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
 }
 
-template <typename TO, bool DUAL>
+constexpr int kMmaStages = 3;
+constexpr size_t mma_shared_bytes(int bm, bool dual) { return sizeof(__nv_bfloat16) * kMmaStages * (bm + (dual ? 2 : 1) * kMmaCols) * kMmaLd; }
+
+// BM: rows of a tile (32: 8 warps as 2 x 4, a warp 16 x 32; 64: 4 x 2, a warp 16 x 64).
+template <typename TO, bool DUAL, int BM>
 __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bfloat16* a, long long lda, const int* source, int divisor,
                                                                  const __nv_bfloat16* w, const __nv_bfloat16* w2, int N, int K, TO* out,
                                                                  long long ldo, const int* tiles, const int* n_tiles) {
@@ -232,11 +249,12 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
     if (tile >= __ldcg(n_tiles)) return;
     const int expert = __ldcg(tiles + 3 * tile), row0 = __ldcg(tiles + 3 * tile + 1), rows = __ldcg(tiles + 3 * tile + 2);
     const int col0 = blockIdx.x * kMmaCols;
-    __shared__ __align__(16) __nv_bfloat16 As[2][kTileRows * kMmaLd];
-    __shared__ __align__(16) __nv_bfloat16 Ws[2][kMmaCols * kMmaLd];
-    __shared__ __align__(16) __nv_bfloat16 W2s[2][DUAL ? kMmaCols * kMmaLd : 8];
-    __shared__ long long arow[kTileRows];
-    if (threadIdx.x < kTileRows) {
+    constexpr int WN = BM == 32 ? 4 : 2;              // warps across the columns
+    constexpr int NP = kMmaCols / WN / 8;             // n8 pieces of a warp
+    constexpr int kStage = (BM + (DUAL ? 2 : 1) * kMmaCols) * kMmaLd;
+    extern __shared__ __align__(16) __nv_bfloat16 staged[];       // per stage: A [BM][kMmaLd], W [128][kMmaLd], W2 the same
+    __shared__ long long arow[BM];
+    if (threadIdx.x < BM) {
         const int r = row0 + min(static_cast<int>(threadIdx.x), rows - 1);
         arow[threadIdx.x] = static_cast<long long>(source ? __ldcg(source + r) / divisor : r) * lda;
     }
@@ -244,47 +262,50 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
     const __nv_bfloat16* we = w + static_cast<size_t>(expert) * N * K;
     const __nv_bfloat16* we2 = DUAL ? w2 + static_cast<size_t>(expert) * N * K : nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int wm = warp >> 2, wn = warp & 3;                 // the warp's 16 rows and 32 columns
-    auto fetch = [&](int k0, int stage) {
-        if (threadIdx.x < kTileRows * 4) {
-            const int r = threadIdx.x >> 2, k = k0 + (threadIdx.x & 3) * 8;
-            mlr_async_copy16(&As[stage][r * kMmaLd + (threadIdx.x & 3) * 8], k < K ? a + arow[r] + k : a, k < K);
-        }
+    const int wm = warp / WN, wn = warp % WN;
+    const int steps = (K + kMmaK - 1) / kMmaK;
+    auto fetch = [&](int step, int stage) {
+        if (step < steps) {
+            const int k0 = step * kMmaK;
+            __nv_bfloat16* As = staged + stage * kStage;
+            __nv_bfloat16* Ws = As + BM * kMmaLd;
+            __nv_bfloat16* W2s = Ws + kMmaCols * kMmaLd;
+            if (threadIdx.x < BM * 4) {
+                const int r = threadIdx.x >> 2, k = k0 + (threadIdx.x & 3) * 8;
+                mlr_async_copy16(&As[r * kMmaLd + (threadIdx.x & 3) * 8], k < K ? a + arow[r] + k : a, k < K);
+            }
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int i = threadIdx.x + 256 * j;
-            const int n = i >> 2, k = k0 + (i & 3) * 8;
-            const bool real = col0 + n < N && k < K;
-            const size_t at = static_cast<size_t>(col0 + n) * K + k;
-            mlr_async_copy16(&Ws[stage][n * kMmaLd + (i & 3) * 8], real ? we + at : we, real);
-            if (DUAL) mlr_async_copy16(&W2s[stage][n * kMmaLd + (i & 3) * 8], real ? we2 + at : we2, real);
+            for (int j = 0; j < 2; ++j) {
+                const int i = threadIdx.x + 256 * j;
+                const int n = i >> 2, k = k0 + (i & 3) * 8;
+                const bool real = col0 + n < N && k < K;
+                const size_t at = static_cast<size_t>(col0 + n) * K + k;
+                mlr_async_copy16(&Ws[n * kMmaLd + (i & 3) * 8], real ? we + at : we, real);
+                if (DUAL) mlr_async_copy16(&W2s[n * kMmaLd + (i & 3) * 8], real ? we2 + at : we2, real);
+            }
         }
         mlr_async_commit();
     };
-    float acc[4][4] = {}, acc2[DUAL ? 4 : 1][4] = {};
-    const int steps = (K + kMmaK - 1) / kMmaK;
-    fetch(0, 0);
+    float acc[NP][4] = {}, acc2[DUAL ? NP : 1][4] = {};
+#pragma unroll
+    for (int st = 0; st < kMmaStages - 1; ++st) fetch(st, st);
     // ldmatrix addresses of this lane: A rows (lane & 15) at k (lane >> 4) * 8; W rows n = (lane & 7) + (lane >> 4) * 8 at k ((lane >> 3) & 1) * 8.
     const int a_off = (wm * 16 + (lane & 15)) * kMmaLd + (lane >> 4) * 8;
-    const int b_off = (wn * 32 + (lane & 7) + (lane >> 4) * 8) * kMmaLd + ((lane >> 3) & 1) * 8;
+    const int b_off = (wn * NP * 8 + (lane & 7) + (lane >> 4) * 8) * kMmaLd + ((lane >> 3) & 1) * 8;
     for (int step = 0; step < steps; ++step) {
-        const int stage = step & 1;
-        if (step + 1 < steps) {
-            fetch((step + 1) * kMmaK, stage ^ 1);
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-        } else {
-            mlr_async_wait();
-        }
-        __syncthreads();
-        const uint32_t a_base = static_cast<uint32_t>(__cvta_generic_to_shared(&As[stage][0]));
-        const uint32_t b_base = static_cast<uint32_t>(__cvta_generic_to_shared(&Ws[stage][0]));
-        const uint32_t b2_base = static_cast<uint32_t>(__cvta_generic_to_shared(&W2s[stage][0]));
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(kMmaStages - 2) : "memory");
+        __syncthreads();          // this step's stage has landed for everyone, and everyone is done with the stage fetched next
+        fetch(step + kMmaStages - 1, (step + kMmaStages - 1) % kMmaStages);
+        const __nv_bfloat16* As = staged + (step % kMmaStages) * kStage;
+        const uint32_t a_base = static_cast<uint32_t>(__cvta_generic_to_shared(As));
+        const uint32_t b_base = a_base + 2 * BM * kMmaLd;
+        const uint32_t b2_base = b_base + 2 * kMmaCols * kMmaLd;
 #pragma unroll
         for (int ks = 0; ks < kMmaK / 16; ++ks) {
             uint32_t fa[4];
             ldmatrix_x4(fa, a_base + 2 * (a_off + ks * 16));
 #pragma unroll
-            for (int pair = 0; pair < 2; ++pair) {
+            for (int pair = 0; pair < NP / 2; ++pair) {
                 uint32_t fb[4];
                 ldmatrix_x4(fb, b_base + 2 * (b_off + pair * 16 * kMmaLd + ks * 16));
                 mma_bf16(acc[2 * pair], fa, fb[0], fb[1]);
@@ -296,15 +317,15 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
                 }
             }
         }
-        __syncthreads();
     }
+    mlr_async_wait();
     mlr_grid_dependents_may_start();
 #pragma unroll
-    for (int piece = 0; piece < 4; ++piece)
+    for (int piece = 0; piece < NP; ++piece)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int r = wm * 16 + (lane >> 2) + 8 * half;
-            const int c = col0 + wn * 32 + piece * 8 + (lane & 3) * 2;
+            const int c = col0 + wn * NP * 8 + piece * 8 + (lane & 3) * 2;
             if (r >= rows) continue;
             TO* orow = out + static_cast<size_t>(row0 + r) * ldo;
 #pragma unroll
@@ -323,12 +344,17 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* y, long long 
                                                       long long ldo, int width) {
     mlr_grid_wait();
     const int row = blockIdx.x;
+    __shared__ float weight[kMaxTop];
+    __shared__ long long from[kMaxTop];
+    if (threadIdx.x < top) {
+        weight[threadIdx.x] = __ldcg(weights + row * top + threadIdx.x);
+        from[threadIdx.x] = static_cast<long long>(__ldcg(row_of_pair + row * top + threadIdx.x)) * ldy;
+    }
+    __syncthreads();
     for (int c = threadIdx.x; c < width; c += 256) {
         float sum = 0.0f;
-        for (int j = 0; j < top; ++j) {
-            const int p = row * top + j;
-            sum = fmaf(__ldcg(weights + p), __ldcg(y + static_cast<size_t>(__ldcg(row_of_pair + p)) * ldy + c), sum);
-        }
+#pragma unroll 4
+        for (int j = 0; j < top; ++j) sum = fmaf(weight[j], __ldcg(y + from[j] + c), sum);
         if (shared_y) {
             const float v = mlr_load(shared_y + static_cast<size_t>(row) * ld_shared, c);
             sum = shared_gate ? fmaf(__ldcg(shared_gate + row), v, sum) : sum + v;
@@ -367,13 +393,15 @@ MLR_API int mlr_experts_route(const void* x, long long ld, int act_bf16, const f
 }
 
 // tiles: int32 [3 * (pairs / 32 + experts)]; first_row: int32 [experts + 1]; n_tiles: int32 [1]; row_of_pair, pair_of_row: int32 [pairs].
-MLR_API int mlr_experts_arrange(int* counts, const int* chosen, const int* place, int experts, int rows, int top, int* first_row, int* tiles,
-                                int* n_tiles, int* row_of_pair, int* pair_of_row, cudaStream_t stream) {
+// tile_rows: 32, or 64 (the tensor-core products of many rows; the products must be told the same).
+MLR_API int mlr_experts_arrange(int* counts, const int* chosen, const int* place, int experts, int rows, int top, int tile_rows, int* first_row,
+                                int* tiles, int* n_tiles, int* row_of_pair, int* pair_of_row, cudaStream_t stream) {
+    MLR_REQUIRE(tile_rows == 32 || tile_rows == 64, "experts_arrange: tiles of 32 or 64 rows, not %d", tile_rows);
     MLR_REQUIRE(counts && chosen && place && first_row && tiles && n_tiles && row_of_pair && pair_of_row && experts >= 1 && experts <= kMaxExperts,
                 "experts_arrange: bad arguments");
     if (rows <= 0) return 0;
-    mlr_launch(arrange_kernel, dim3(1), dim3(1024), 0, stream, counts, chosen, place, experts, rows * top, first_row, tiles, n_tiles, row_of_pair,
-               pair_of_row);
+    mlr_launch(arrange_kernel, dim3(1), dim3(1024), 0, stream, counts, chosen, place, experts, rows * top, tile_rows, first_row, tiles, n_tiles,
+               row_of_pair, pair_of_row);
     return mlr_launched("experts_arrange");
 }
 
@@ -386,35 +414,49 @@ static bool mlr_experts_simt_only() {
     return only;
 }
 
-// The most tiles `pairs` rows of `experts` experts can make (the size of the grid, and of `tiles` / 3).
+// The most tiles `pairs` rows of `experts` experts can make (the size of the grid, and of `tiles` / 3), whichever the tile's rows.
 MLR_API int mlr_experts_max_tiles(int pairs, int experts) { return pairs / kTileRows + experts; }
+
+// Whether the tensor-core product takes these sizes (bfloat16 activations with rows of K values on 16-byte borders): 1 yes, 0 no.
+MLR_API int mlr_experts_tensor_cores(int K, long long lda) { return K % 8 == 0 && lda % 8 == 0 && !mlr_experts_simt_only(); }
 
 // a: [*, K] activations (bfloat16 or float32), row r of the product is row source[r] / divisor of `a` (or r without `source`).
 // w (and w2 when `gated`): [experts, N, K] in the activations' precision.  out: [pairs, N]; float32 when out_f32, else the
 // activations' precision; with `gated` out = silu(a w^T) * (a w2^T).  The product has rows * top rows.
 MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, const int* source, int divisor, const void* w, const void* w2, int gated,
                                 int N, int K, void* out, long long ldo, int out_f32, const int* tiles, const int* n_tiles, int rows, int top, int experts,
-                                cudaStream_t stream) {
+                                int tile_rows, cudaStream_t stream) {
     const int pairs = rows * top;
     MLR_REQUIRE(a && w && out && tiles && n_tiles && N > 0 && K > 0 && (!gated || w2) && (!source || divisor > 0), "experts_product: bad arguments");
+    const bool tensor_cores = act_bf16 && K % 8 == 0 && lda % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+                              reinterpret_cast<uintptr_t>(w) % 16 == 0 && (!gated || reinterpret_cast<uintptr_t>(w2) % 16 == 0) && !mlr_experts_simt_only();
+    MLR_REQUIRE(tile_rows == 32 || (tile_rows == 64 && tensor_cores), "experts_product: tiles of %d rows are not built for this product", tile_rows);
     if (pairs <= 0) return 0;
     const int max_tiles = mlr_experts_max_tiles(pairs, experts);
     MLR_REQUIRE(max_tiles <= 65535, "experts_product: %d row tiles are more than a grid takes", max_tiles);
     const dim3 grid((N + kTileCols - 1) / kTileCols, max_tiles);
     // bfloat16 rows that start on 16-byte borders go to the tensor cores.
-    if (act_bf16 && K % 8 == 0 && lda % 8 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
-        (!gated || reinterpret_cast<uintptr_t>(w2) % 16 == 0) && !mlr_experts_simt_only()) {
+    if (tensor_cores) {
         const dim3 wide((N + kMmaCols - 1) / kMmaCols, max_tiles);
         const __nv_bfloat16 *ab = static_cast<const __nv_bfloat16*>(a), *wb = static_cast<const __nv_bfloat16*>(w),
                             *w2b = static_cast<const __nv_bfloat16*>(w2);
-        if (gated && !out_f32)
-            mlr_launch((expert_product_mma_kernel<__nv_bfloat16, true>), dim3(wide), dim3(256), 0, stream, ab, lda, source, divisor, wb, w2b, N, K,
-                       static_cast<__nv_bfloat16*>(out), ldo, tiles, n_tiles);
-        else if (!gated && out_f32)
-            mlr_launch((expert_product_mma_kernel<float, false>), dim3(wide), dim3(256), 0, stream, ab, lda, source, divisor, wb, w2b, N, K,
-                       static_cast<float*>(out), ldo, tiles, n_tiles);
-        else
+#define MLR_MMA(TO, DUAL, BM)                                                                                                              \
+    do {                                                                                                                                   \
+        cudaFuncSetAttribute(expert_product_mma_kernel<TO, DUAL, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,                         \
+                             static_cast<int>(mma_shared_bytes(BM, DUAL)));                                                                \
+        mlr_launch((expert_product_mma_kernel<TO, DUAL, BM>), dim3(wide), dim3(256), mma_shared_bytes(BM, DUAL), stream, ab, lda, source,  \
+                   divisor, wb, w2b, N, K, static_cast<TO*>(out), ldo, tiles, n_tiles);                                                    \
+    } while (0)
+        if (gated && !out_f32) {
+            if (tile_rows == 64) MLR_MMA(__nv_bfloat16, true, 64);
+            else MLR_MMA(__nv_bfloat16, true, 32);
+        } else if (!gated && out_f32) {
+            if (tile_rows == 64) MLR_MMA(float, false, 64);
+            else MLR_MMA(float, false, 32);
+        } else {
             return mlr_fail("experts_product: this pair of precisions is not built");
+        }
+#undef MLR_MMA
         return mlr_launched("experts_product");
     }
 #define MLR_GO(T, TO, DUAL)                                                                                                              \

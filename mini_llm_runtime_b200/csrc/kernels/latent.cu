@@ -61,7 +61,17 @@ __global__ void __launch_bounds__(kThreads) head_project_kernel(const T* x, long
     if (b >= B) return;
     const T* wh = w + static_cast<size_t>(head) * A * B + b;
     float acc[kRows] = {};
-    for (int a = 0; a < A; ++a) {
+    int a = 0;
+    for (; a + 8 <= A; a += 8) {          // eight loads of the matrix in flight
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = mlr_load(wh, static_cast<size_t>(a + i) * B);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) acc[r] = fmaf(xs[r * A + a + i], v[i], acc[r]);
+    }
+    for (; a < A; ++a) {
         const float v = mlr_load(wh, static_cast<size_t>(a) * B);
 #pragma unroll
         for (int r = 0; r < kRows; ++r) acc[r] = fmaf(xs[r * A + a], v, acc[r]);

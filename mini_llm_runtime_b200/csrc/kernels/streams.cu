@@ -26,14 +26,18 @@ struct StreamWeights {
     float in[kMaxStreams];
 };
 
-template <typename TO>
+// S: the number of copies when it is at most 8 (weights in registers, loops unrolled), or 0 for any number up to kMaxStreams
+// (weights in shared memory).  V: columns a thread takes at a time (4 when the width and all strides allow 16-byte accesses).
+template <typename TO, int S, int V>
 __global__ void __launch_bounds__(kThreads) streams_step_kernel(float* h, const float* y, long long ld_y, const float* y_scale, const float* mix,
                                                                  const float* w_out, const float* w_in, const float* norm_weight, float eps,
-                                                                 TO* out, long long ld_out, const int* rows, int width, int streams) {
+                                                                 TO* out, long long ld_out, const int* rows, int width, int streams_given) {
     mlr_grid_wait();
     extern __shared__ __align__(16) float u[];          // [width]
     __shared__ float scratch[32];
     __shared__ StreamWeights w;
+    constexpr int kCopies = S ? S : kMaxStreams;
+    const int streams = S ? S : streams_given;
     const int row = rows ? rows[blockIdx.x] : blockIdx.x;
     if (threadIdx.x < streams * streams && mix) w.mix[threadIdx.x] = mix[threadIdx.x];
     if (threadIdx.x < streams) {
@@ -41,37 +45,81 @@ __global__ void __launch_bounds__(kThreads) streams_step_kernel(float* h, const 
         w.in[threadIdx.x] = w_in ? w_in[threadIdx.x] : 1.0f;
     }
     __syncthreads();
+    // With a fixed S the weights move to registers (constant indices after unrolling).
+    float rmix[S ? S * S : 1], rout[S ? S : 1], rin[S ? S : 1];
+    if (S) {
+#pragma unroll
+        for (int i = 0; i < S * S; ++i) rmix[i] = y ? w.mix[i] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < S; ++i) {
+            rout[i] = y ? w.out[i] : 0.0f;
+            rin[i] = w.in[i];
+        }
+    }
     float* x = h + static_cast<size_t>(row) * streams * width;
     const float* yrow = y ? y + static_cast<size_t>(row) * ld_y : nullptr;
     float squares = 0.0f;
-    for (int c = threadIdx.x; c < width; c += kThreads) {
-        float old[kMaxStreams];
+    for (int c = threadIdx.x * V; c < width; c += kThreads * V) {
+        float old[kCopies][V];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) old[s] = s < streams ? x[static_cast<size_t>(s) * width + c] : 0.0f;
-        float sum = 0.0f;
+        for (int s = 0; s < kCopies; ++s) {
+            if (s < streams) {
+                if (V == 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(x + static_cast<size_t>(s) * width + c);
+                    old[s][0] = v.x, old[s][1] = v.y, old[s][2] = v.z, old[s][V - 1] = v.w;
+                } else {
+                    old[s][0] = x[static_cast<size_t>(s) * width + c];
+                }
+            }
+        }
+        float sum[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) sum[e] = 0.0f;
         if (yrow) {
-            float add = __ldcg(yrow + c);
-            if (y_scale) add *= y_scale[c];
+            float add[V];
 #pragma unroll
-            for (int t = 0; t < kMaxStreams; ++t) {
+            for (int e = 0; e < V; ++e) {
+                add[e] = __ldcg(yrow + c + e);
+                if (y_scale) add[e] *= y_scale[c + e];
+            }
+#pragma unroll
+            for (int t = 0; t < kCopies; ++t) {
                 if (t < streams) {
-                    float value = 0.0f;
+                    float value[V];
 #pragma unroll
-                    for (int s = 0; s < kMaxStreams; ++s)
-                        if (s < streams) value = fmaf(w.mix[s * streams + t], old[s], value);
-                    value = fmaf(w.out[t], add, value);
-                    x[static_cast<size_t>(t) * width + c] = value;
-                    sum = fmaf(w.in[t], value, sum);
+                    for (int e = 0; e < V; ++e) value[e] = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < kCopies; ++s)
+                        if (s < streams) {
+                            const float m = S ? rmix[S ? s * S + t : 0] : w.mix[s * streams + t];
+#pragma unroll
+                            for (int e = 0; e < V; ++e) value[e] = fmaf(m, old[s][e], value[e]);
+                        }
+                    const float o = S ? rout[S ? t : 0] : w.out[t], in = S ? rin[S ? t : 0] : w.in[t];
+#pragma unroll
+                    for (int e = 0; e < V; ++e) {
+                        value[e] = fmaf(o, add[e], value[e]);
+                        sum[e] = fmaf(in, value[e], sum[e]);
+                    }
+                    if (V == 4) *reinterpret_cast<float4*>(x + static_cast<size_t>(t) * width + c) = make_float4(value[0], value[1], value[2], value[V - 1]);
+                    else x[static_cast<size_t>(t) * width + c] = value[0];
                 }
             }
         } else {
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
-                if (s < streams) sum = fmaf(w.in[s], old[s], sum);
+            for (int s = 0; s < kCopies; ++s)
+                if (s < streams) {
+                    const float in = S ? rin[S ? s : 0] : w.in[s];
+#pragma unroll
+                    for (int e = 0; e < V; ++e) sum[e] = fmaf(in, old[s][e], sum[e]);
+                }
         }
         if (out) {
-            u[c] = sum;
-            squares = fmaf(sum, sum, squares);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                u[c + e] = sum[e];
+                squares = fmaf(sum[e], sum[e], squares);
+            }
         }
     }
     if (!out) {
@@ -143,15 +191,35 @@ MLR_API int mlr_streams_step(float* h, const float* y, long long ld_y, const flo
     MLR_REQUIRE(static_cast<size_t>(width) * sizeof(float) <= 200 * 1024, "streams_step: a width of %d does not fit shared memory", width);
     if (count <= 0) return 0;
     const size_t shared = out ? static_cast<size_t>(width) * sizeof(float) : 0;
-    if (out_bf16) {
-        if (shared > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        mlr_launch((streams_step_kernel<__nv_bfloat16>), dim3(count), dim3(kThreads), shared, stream, h, y, ld_y, y_scale, mix, w_out, w_in,
-                   norm_weight, eps, static_cast<__nv_bfloat16*>(out), ld_out, rows, width, streams);
-    } else {
-        if (shared > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        mlr_launch((streams_step_kernel<float>), dim3(count), dim3(kThreads), shared, stream, h, y, ld_y, y_scale, mix, w_out, w_in, norm_weight,
-                   eps, static_cast<float*>(out), ld_out, rows, width, streams);
+    const bool wide = width % 4 == 0 && reinterpret_cast<uintptr_t>(h) % 16 == 0;
+#define MLR_GO(TO, S, V)                                                                                                                   \
+    do {                                                                                                                                   \
+        if (shared > 48 * 1024)                                                                                                            \
+            cudaFuncSetAttribute(streams_step_kernel<TO, S, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));    \
+        mlr_launch((streams_step_kernel<TO, S, V>), dim3(count), dim3(kThreads), shared, stream, h, y, ld_y, y_scale, mix, w_out, w_in,    \
+                   norm_weight, eps, static_cast<TO*>(out), ld_out, rows, width, streams);                                                 \
+    } while (0)
+#define MLR_PICK(TO, S)                  \
+    do {                                 \
+        if (wide) MLR_GO(TO, S, 4);      \
+        else MLR_GO(TO, S, 1);           \
+    } while (0)
+#define MLR_COPIES(TO)                                     \
+    switch (streams) {                                     \
+        case 1: MLR_PICK(TO, 1); break;                    \
+        case 2: MLR_PICK(TO, 2); break;                    \
+        case 3: MLR_PICK(TO, 3); break;                    \
+        case 4: MLR_PICK(TO, 4); break;                    \
+        case 5: MLR_PICK(TO, 5); break;                    \
+        case 6: MLR_PICK(TO, 6); break;                    \
+        case 7: MLR_PICK(TO, 7); break;                    \
+        case 8: MLR_PICK(TO, 8); break;                    \
+        default: MLR_GO(TO, 0, 1); break;                  \
     }
+    if (out_bf16) { MLR_COPIES(__nv_bfloat16) } else { MLR_COPIES(float) }
+#undef MLR_COPIES
+#undef MLR_PICK
+#undef MLR_GO
     return mlr_launched("streams_step");
 }
 

@@ -87,15 +87,20 @@ class RoutedExperts(FeedForward):
         b.launch("experts", "mlr_experts_route", x.ptr, x.ld, x.is_bf16, self.router.data_ptr(), self.correction.data_ptr(), rows,
                  self.width, E, self.groups, self.keep, top, int(bool(self.shared_inter)), chosen.ptr, weights.ptr, place.ptr,
                  self.counts.data_ptr(), gate.ptr if gate else None, b.stream)
-        b.launch("experts", "mlr_experts_arrange", self.counts.data_ptr(), chosen.ptr, place.ptr, E, rows, top, first_row.ptr, tiles.ptr,
-                 n_tiles.ptr, row_of_pair.ptr, pair_of_row.ptr, b.stream)
+        # Tiles of 64 rows for the tensor-core products once an expert gets that many rows on average; 32 otherwise (a decode
+        # step's few rows per expert, the float32 path, rows that do not start on 16-byte borders).
+        lib = native.module("experts")
+        both = rt.is_bf16 and lib.mlr_experts_tensor_cores(self.width, x.ld) and lib.mlr_experts_tensor_cores(self.inter, self.inter)
+        tile_rows = 64 if both and b.ge(rows, max(1, 64 * E // top)) else 32
+        b.launch("experts", "mlr_experts_arrange", self.counts.data_ptr(), chosen.ptr, place.ptr, E, rows, top, tile_rows, first_row.ptr,
+                 tiles.ptr, n_tiles.ptr, row_of_pair.ptr, pair_of_row.ptr, b.stream)
         act = b.temp(rows, top * self.inter, rt.dtype)             # [rows * top, inter], rows in the order by expert
         b.launch("experts", "mlr_experts_product", x.ptr, x.ld, x.is_bf16, pair_of_row.ptr, top, self.w_gate.data_ptr(),
                  self.w_up.data_ptr(), 1, self.inter, self.width, act.ptr, self.inter, int(not rt.is_bf16), tiles.ptr, n_tiles.ptr, rows,
-                 top, E, b.stream)
+                 top, E, tile_rows, b.stream)
         y = b.temp(rows, top * self.width, f32)
         b.launch("experts", "mlr_experts_product", act.ptr, self.inter, x.is_bf16, None, 1, self.w_down.data_ptr(), None, 0, self.width,
-                 self.inter, y.ptr, self.width, 1, tiles.ptr, n_tiles.ptr, rows, top, E, b.stream)
+                 self.inter, y.ptr, self.width, 1, tiles.ptr, n_tiles.ptr, rows, top, E, tile_rows, b.stream)
         shared = None
         if self.shared_inter:
             hidden = rt.gated_linear(b, x, self.shared_gate_up)
