@@ -236,18 +236,31 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) 
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
 }
 
-constexpr int kMmaStages = 3;
-constexpr size_t mma_shared_bytes(int bm, bool dual) { return sizeof(__nv_bfloat16) * kMmaStages * (bm + (dual ? 2 : 1) * kMmaCols) * kMmaLd; }
+// Stages of the copy pipeline: a tile of 32 rows belongs to a step of few rows, whose blocks are fewer than the SMs and wait
+// for memory: five stages keep more bytes in flight; tiles of 64 rows leave room for two blocks an SM with three.
+__host__ __device__ constexpr int mma_stages(int bm) { return bm == 32 ? 5 : 3; }
+constexpr size_t mma_shared_bytes(int bm, bool dual) { return sizeof(__nv_bfloat16) * mma_stages(bm) * (bm + (dual ? 2 : 1) * kMmaCols) * kMmaLd; }
 
 // BM: rows of a tile (32: 8 warps as 2 x 4, a warp 16 x 32; 64: 4 x 2, a warp 16 x 64).
 template <typename TO, bool DUAL, int BM>
 __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bfloat16* a, long long lda, const int* source, int divisor,
                                                                  const __nv_bfloat16* w, const __nv_bfloat16* w2, int N, int K, TO* out,
-                                                                 long long ldo, const int* tiles, const int* n_tiles) {
+                                                                 long long ldo, const int* tiles, const int* n_tiles, int all_rows,
+                                                                 int a_step, int out_step) {
     mlr_grid_wait();
-    const int tile = blockIdx.y;
-    if (tile >= __ldcg(n_tiles)) return;
-    const int expert = __ldcg(tiles + 3 * tile), row0 = __ldcg(tiles + 3 * tile + 1), rows = __ldcg(tiles + 3 * tile + 2);
+    // With a tile list: tile blockIdx.y of it.  Without: every matrix (blockIdx.z) takes all `all_rows` rows, its inputs `a_step`
+    // columns and its outputs `out_step` columns further right than those of the matrix before.
+    constexpr int kMmaStages = mma_stages(BM);
+    int expert, row0, rows;
+    if (tiles) {
+        const int tile = blockIdx.y;
+        if (tile >= __ldcg(n_tiles)) return;
+        expert = __ldcg(tiles + 3 * tile), row0 = __ldcg(tiles + 3 * tile + 1), rows = __ldcg(tiles + 3 * tile + 2);
+    } else {
+        expert = blockIdx.z, row0 = blockIdx.y * BM, rows = min(BM, all_rows - row0);
+        a += static_cast<size_t>(expert) * a_step;
+        out += static_cast<size_t>(expert) * out_step;
+    }
     const int col0 = blockIdx.x * kMmaCols;
     constexpr int WN = BM == 32 ? 4 : 2;              // warps across the columns
     constexpr int NP = kMmaCols / WN / 8;             // n8 pieces of a warp
@@ -445,7 +458,7 @@ MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, cons
         cudaFuncSetAttribute(expert_product_mma_kernel<TO, DUAL, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,                         \
                              static_cast<int>(mma_shared_bytes(BM, DUAL)));                                                                \
         mlr_launch((expert_product_mma_kernel<TO, DUAL, BM>), dim3(wide), dim3(256), mma_shared_bytes(BM, DUAL), stream, ab, lda, source,  \
-                   divisor, wb, w2b, N, K, static_cast<TO*>(out), ldo, tiles, n_tiles);                                                    \
+                   divisor, wb, w2b, N, K, static_cast<TO*>(out), ldo, tiles, n_tiles, 0, 0, 0);                                           \
     } while (0)
         if (gated && !out_f32) {
             if (tile_rows == 64) MLR_MMA(__nv_bfloat16, true, 64);
@@ -472,6 +485,32 @@ MLR_API int mlr_experts_product(const void* a, long long lda, int act_bf16, cons
     }
 #undef MLR_GO
     return mlr_launched("experts_product");
+}
+
+// The same tensor-core product for `count` matrices that all take the same rows (the heads of a per-head projection):
+// out[m, i * N + n] = sum_k a[m, i * K + k] w[i, n, k], bfloat16 in and out.  Returns 2 (and launches nothing) for sizes it does not take.
+MLR_API int mlr_batched_product_bf16(const void* a, long long lda, const void* w, void* out, long long ldo, int rows, int count, int N, int K,
+                                     cudaStream_t stream) {
+    MLR_REQUIRE(a && w && out && count > 0 && count <= 65535 && N > 0 && K > 0, "batched_product: bad arguments");
+    if (K % 8 || lda % 8 || reinterpret_cast<uintptr_t>(a) % 16 || reinterpret_cast<uintptr_t>(w) % 16 || mlr_experts_simt_only()) return 2;
+    if (rows <= 0) return 0;
+    const __nv_bfloat16 *ab = static_cast<const __nv_bfloat16*>(a), *wb = static_cast<const __nv_bfloat16*>(w);
+    const int* none = nullptr;
+    if (rows > 32) {
+        const dim3 grid((N + kMmaCols - 1) / kMmaCols, (rows + 63) / 64, count);
+        MLR_REQUIRE(grid.y <= 65535, "batched_product: too many rows");
+        cudaFuncSetAttribute(expert_product_mma_kernel<__nv_bfloat16, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(mma_shared_bytes(64, false)));
+        mlr_launch((expert_product_mma_kernel<__nv_bfloat16, false, 64>), dim3(grid), dim3(256), mma_shared_bytes(64, false), stream, ab, lda, none, 1,
+                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, K, N);
+    } else {
+        const dim3 grid((N + kMmaCols - 1) / kMmaCols, 1, count);
+        cudaFuncSetAttribute(expert_product_mma_kernel<__nv_bfloat16, false, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(mma_shared_bytes(32, false)));
+        mlr_launch((expert_product_mma_kernel<__nv_bfloat16, false, 32>), dim3(grid), dim3(256), mma_shared_bytes(32, false), stream, ab, lda, none, 1,
+                   wb, wb, N, K, static_cast<__nv_bfloat16*>(out), ldo, none, none, rows, K, N);
+    }
+    return mlr_launched("batched_product");
 }
 
 MLR_API int mlr_experts_combine(const float* y, long long ldy, const int* row_of_pair, const float* weights, int top, const void* shared_y,

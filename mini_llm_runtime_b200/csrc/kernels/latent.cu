@@ -7,8 +7,9 @@
 // two row-wise pieces around it:
 //
 //   mlr_latent_cache    c = rmsnorm(row of the down projection) * weight, float32 math, into the token's place
-//                       of its page ([page][token_in_page][rank], one kv head, keys only) and, if asked, a buffer
-//   mlr_head_project    y[m, h, :] = x[m, h, :] W_h,  W [heads, A, B] row-major, float32 sums in the order a = 0..A-1
+//                       of its page ([page][token_in_page][rank], one kv head, keys only)
+//   mlr_head_project    y[m, h, :] = x[m, h, :] W_h,  W [heads, A, B] row-major, float32 sums in the order a = 0..A-1 (the
+//                       float32 path and odd sizes; bfloat16 rows on 16-byte borders take `mlr_batched_product_bf16` of experts.cu)
 #include "common.cuh"
 
 namespace {

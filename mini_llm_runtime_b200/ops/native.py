@@ -122,6 +122,7 @@ _SIGNATURES = {
         "mlr_experts_arrange": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p],
         "mlr_experts_tensor_cores": [c_int, c_longlong],
+        "mlr_batched_product_bf16": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p],
         "mlr_experts_max_tiles": [c_int, c_int],
         "mlr_experts_product": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                 c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

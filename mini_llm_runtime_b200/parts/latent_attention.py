@@ -57,7 +57,15 @@ class LatentAttentionMixer(Mixer):
         return specs
 
     def kernel_modules(self, dtype) -> List[str]:
-        return ["latent", "attention_masked"] + F.product_modules(dtype)
+        return ["latent", "attention_masked"] + (["experts"] if dtype is torch.bfloat16 else []) + F.product_modules(dtype)
+
+    def _per_head(self, b, x, w, w_t, y, inputs: int, outputs: int) -> None:
+        """y[m, h, :] = x[m, h, :] W_h: on the tensor cores (the batched product of `experts.cu`) for bfloat16 rows on 16-byte
+        borders, else on the CUDA cores."""
+        if b.rt.is_bf16 and native.module("experts").mlr_experts_tensor_cores(inputs, x.ld) and x.ptr % 16 == 0:
+            b.launch("experts", "mlr_batched_product_bf16", x.ptr, x.ld, w_t.data_ptr(), y.ptr, y.ld, x.rows, self.heads, outputs, inputs, b.stream)
+        else:
+            b.launch("latent", "mlr_head_project", x.ptr, x.ld, w.data_ptr(), y.ptr, y.ld, x.is_bf16, x.rows, self.heads, inputs, outputs, b.stream)
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         w = self.spec.weights
@@ -67,6 +75,9 @@ class LatentAttentionMixer(Mixer):
         # [heads, D, R] as stored; [heads, R, Dv] transposed, so that both per-head products read rows of their matrix.
         self.w_uk = rt.matrix(tensors[w["uk"]]).view(self.heads, self.dim, self.rank).contiguous()
         self.w_uv = rt.matrix(tensors[w["uv"]]).view(self.heads, self.vdim, self.rank).transpose(1, 2).contiguous()
+        # The same two as [heads, outputs, inputs], the operand layout of the tensor-core product (bfloat16 only).
+        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous() if rt.is_bf16 else None
+        self.w_uv_t = self.w_uv.transpose(1, 2).contiguous() if rt.is_bf16 else None
         self.latent_weight = rt.vector(tensors[w["dkv_norm"]]).float().contiguous() if self.own_latent else None
         self.desc = MaskedAttentionSpec(freq=None, heads=self.heads, kv_heads=1, dim=self.rank, vdim=self.rank, rot_dims=0, window=0,
                                         chunk=0, sink=0, gate_kind=GATES[None], shared_kv=1, scale=self.scale, out_scale=1.0)
@@ -86,13 +97,11 @@ class LatentAttentionMixer(Mixer):
                      b.table_stride(run.group), b.page_size, rows, b.status, b.stream)
         wide = self.heads * self.rank
         q = b.temp(rows, wide, rt.dtype)
-        b.launch("latent", "mlr_head_project", proj.ptr, proj.ld, self.w_uk.data_ptr(), q.ptr, q.ld, proj.is_bf16, rows, self.heads, self.dim,
-                 self.rank, b.stream)
+        self._per_head(b, proj, self.w_uk, self.w_uk_t, q, self.dim, self.rank)
         mixed = b.temp(rows, wide, rt.dtype)
         emit_masked_attention(b, self.desc, q, None, mixed, run)
         act = b.temp(rows, self.heads * self.vdim, rt.dtype)
-        b.launch("latent", "mlr_head_project", mixed.ptr, mixed.ld, self.w_uv.data_ptr(), act.ptr, act.ld, proj.is_bf16, rows, self.heads,
-                 self.rank, self.vdim, b.stream)
+        self._per_head(b, mixed, self.w_uv, self.w_uv_t, act, self.rank, self.vdim)
         return rt.linear(b, act, self.w_out, out_dtype=torch.float32)
 
 

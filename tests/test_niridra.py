@@ -283,6 +283,22 @@ def test_per_head_projection_kernel(dtype, heads, A, B, rows):
     assert torch.allclose(y.double().cpu(), want, **tol)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,A,B,rows", [(3, 8, 24, 5), (2, 40, 130, 33), (16, 128, 64, 200), (1, 16, 8, 64), (4, 64, 256, 31)])
+def test_per_head_projection_on_the_tensor_cores(heads, A, B, rows):
+    """The bfloat16 form: one tensor-core product per head over all rows, matrices as [heads, outputs, inputs]."""
+    from mini_llm_runtime_b200.ops import native
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(A + rows)
+    x = torch.randn(rows, heads * A + 8, generator=g).bfloat16().to(dev)
+    w = (torch.randn(heads, B, A, generator=g) / math.sqrt(A)).bfloat16().to(dev)
+    y = torch.full((rows, heads * B + 3), float("nan"), dtype=torch.bfloat16, device=dev)
+    _call("experts", "mlr_batched_product_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), y.data_ptr(), y.stride(0), rows, heads, B, A, native.stream())
+    want = torch.einsum("mha,hba->mhb", x[:, :heads * A].double().cpu().view(rows, heads, A), w.double().cpu()).reshape(rows, heads * B)
+    assert torch.allclose(y[:, :heads * B].double().cpu(), want, atol=2e-2, rtol=2e-2)
+    assert torch.isnan(y[:, heads * B:].float()).all()
+
+
 def _latent_attention_case(dtype, heads, rank, T, page, loud=None, last_rows=None):
     """Latents of one request written into shuffled pages by `mlr_latent_cache`, then attention of every row (or of the
     last rows only) with the latents as keys and values of one shared kv head.  `loud`: a position whose latent is made
