@@ -33,7 +33,7 @@ namespace {
 
 constexpr int kTile = 64;
 constexpr int kThreads = 128;
-constexpr int kMaxDimsPerThread = 2;  // vdim <= 256
+constexpr int kMaxDimsPerThread = 8;  // vdim <= 1024; the kernels are built for 2 (vdim <= 256), 4 and 8 value columns a thread
 constexpr int kRowsPerItem = 16;      // a segment that the planner gives the row kernel brings at most this many rows
 
 template <typename T>
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(kThreads) kv_rope_cache_kernel(const T* k, int
     mlr_grid_dependents_may_start();
 }
 
-template <typename T>
+template <typename T, int DPT>
 __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, int ldq, const T* gate, int ld_gate, T* out, int ldo,
                                                                     const T* cache, int num_pages, const int* positions,
                                                                     const int* segment_of_row, const int* block_table,
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     // into ranges of `split_keys` (from the 64-key border at or below the first one); blockIdx.z names this block's
     // range, whose maximum, sum and weighted values go to `partial` for `attention_masked_merge_kernel` (the sink too).
     float running_max = (s.sink && !partial) ? 0.0f : -INFINITY, running_sum = (s.sink && !partial) ? 1.0f : 0.0f;
-    float acc[kMaxDimsPerThread] = {0.0f, 0.0f};
+    float acc[DPT] = {};
     int tile_first = (lo / kTile) * kTile, tile_last = position;
     if (partial) {
         tile_first += blockIdx.z * split_keys;
@@ -218,14 +218,14 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
             const float alpha = running_max == -INFINITY ? 0.0f : expf(running_max - new_max);
             running_sum *= alpha;
 #pragma unroll
-            for (int d = 0; d < kMaxDimsPerThread; ++d) acc[d] *= alpha;
+            for (int d = 0; d < DPT; ++d) acc[d] *= alpha;
             for (int i0 = 0; i0 < kTile; i0 += 8) {       // eight keys' values are on their way before the first is used
-                float values[8][kMaxDimsPerThread];
+                float values[8][DPT];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const long long offset = offsets[i0 + u];
 #pragma unroll
-                    for (int d = 0; d < kMaxDimsPerThread; ++d) {
+                    for (int d = 0; d < DPT; ++d) {
                         const int c = threadIdx.x + d * kThreads;
                         values[u][d] = (offset >= 0 && c < s.vdim) ? mlr_load(cache + offset, c) : 0.0f;
                     }
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
                     const float w = scores[i0 + u];         // 0 for a key that is not seen
                     running_sum += w;
 #pragma unroll
-                    for (int d = 0; d < kMaxDimsPerThread; ++d) acc[d] = fmaf(w, values[u][d], acc[d]);
+                    for (int d = 0; d < DPT; ++d) acc[d] = fmaf(w, values[u][d], acc[d]);
                 }
             }
             running_max = new_max;
@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
             mine[1] = running_sum;
         }
 #pragma unroll
-        for (int d = 0; d < kMaxDimsPerThread; ++d) {
+        for (int d = 0; d < DPT; ++d) {
             const int c = threadIdx.x + d * kThreads;
             if (c < s.vdim) mine[2 + c] = acc[d];
         }
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
     T* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
     const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * s.vdim : nullptr;
 #pragma unroll
-    for (int d = 0; d < kMaxDimsPerThread; ++d) {
+    for (int d = 0; d < DPT; ++d) {
         const int c = threadIdx.x + d * kThreads;
         if (c < s.vdim) {
             float value = running_sum > 0.0f ? acc[d] / running_sum : 0.0f;
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_kernel(const T* q, 
 }
 
 // Adds up the key ranges of every row of a segment: grid (segments of few rows, heads), as the row kernel's.
-template <typename T>
+template <typename T, int DPT>
 __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const float* partial, const T* gate, int ld_gate, T* out, int ldo,
                                                                           const int* positions, MaskedAttentionSpec s, const int* items,
                                                                           const int* segment_info, int split_keys, int max_splits) {
@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
     float top = s.sink ? 0.0f : -INFINITY;
     for (int i = 0; i < splits; ++i) top = fmaxf(top, __ldcg(mine + static_cast<size_t>(i) * (s.vdim + 2)));
     float sum = s.sink ? expf(-top) : 0.0f;
-    float acc[kMaxDimsPerThread] = {0.0f, 0.0f};
+    float acc[DPT] = {};
     for (int i = 0; i < splits; ++i) {
         const float* part = mine + static_cast<size_t>(i) * (s.vdim + 2);
         const float m = __ldcg(part);
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
         const float w = expf(m - top);
         sum = fmaf(__ldcg(part + 1), w, sum);
 #pragma unroll
-        for (int d = 0; d < kMaxDimsPerThread; ++d) {
+        for (int d = 0; d < DPT; ++d) {
             const int c = threadIdx.x + d * kThreads;
             if (c < s.vdim) acc[d] = fmaf(__ldcg(part + 2 + c), w, acc[d]);
         }
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(kThreads) attention_masked_merge_kernel(const 
     T* orow = out + static_cast<size_t>(row) * ldo + static_cast<size_t>(head) * s.vdim;
     const T* grow = gate ? gate + static_cast<size_t>(row) * ld_gate + static_cast<size_t>(head) * s.vdim : nullptr;
 #pragma unroll
-    for (int d = 0; d < kMaxDimsPerThread; ++d) {
+    for (int d = 0; d < DPT; ++d) {
         const int c = threadIdx.x + d * kThreads;
         if (c < s.vdim) {
             float value = sum > 0.0f ? acc[d] / sum : 0.0f;
@@ -658,26 +658,27 @@ MLR_API int mlr_attention_masked(const MaskedAttentionSpec* spec, const void* q,
     const size_t shared = sizeof(float) * (spec->dim + kTile) + sizeof(long long) * kTile + 16;
     const dim3 grid(rows, spec->heads, max_splits);
     const dim3 merge_grid(rows, spec->heads);
-    if (act_bf16)
-        mlr_launch((attention_masked_kernel<__nv_bfloat16>), dim3(grid), dim3(kThreads), shared, stream,
-                   static_cast<const __nv_bfloat16*>(q), ldq, static_cast<const __nv_bfloat16*>(gate), ld_gate,
-                   static_cast<__nv_bfloat16*>(out), ldo, static_cast<const __nv_bfloat16*>(cache), num_pages, positions, segment_of_row,
-                   block_table, table_stride, page_size, *spec, items, segment_info, split_keys, max_splits, partial, status);
-    else
-        mlr_launch((attention_masked_kernel<float>), dim3(grid), dim3(kThreads), shared, stream, static_cast<const float*>(q), ldq,
-                   static_cast<const float*>(gate), ld_gate, static_cast<float*>(out), ldo, static_cast<const float*>(cache), num_pages,
-                   positions, segment_of_row, block_table, table_stride, page_size, *spec, items, segment_info, split_keys, max_splits,
-                   partial, status);
-    if (partial) {
-        if (act_bf16)
-            mlr_launch((attention_masked_merge_kernel<__nv_bfloat16>), dim3(merge_grid), dim3(kThreads), 0, stream, partial,
-                       static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(out), ldo, positions, *spec, items,
-                       segment_info, split_keys, max_splits);
-        else
-            mlr_launch((attention_masked_merge_kernel<float>), dim3(merge_grid), dim3(kThreads), 0, stream, partial,
-                       static_cast<const float*>(gate), ld_gate, static_cast<float*>(out), ldo, positions, *spec, items, segment_info,
-                       split_keys, max_splits);
-    }
+#define MLR_ROWS(T, DPT)                                                                                                                    \
+    do {                                                                                                                                    \
+        mlr_launch((attention_masked_kernel<T, DPT>), dim3(grid), dim3(kThreads), shared, stream, static_cast<const T*>(q), ldq,            \
+                   static_cast<const T*>(gate), ld_gate, static_cast<T*>(out), ldo, static_cast<const T*>(cache), num_pages, positions,     \
+                   segment_of_row, block_table, table_stride, page_size, *spec, items, segment_info, split_keys, max_splits, partial,       \
+                   status);                                                                                                                 \
+        if (partial)                                                                                                                        \
+            mlr_launch((attention_masked_merge_kernel<T, DPT>), dim3(merge_grid), dim3(kThreads), 0, stream, partial,                       \
+                       static_cast<const T*>(gate), ld_gate, static_cast<T*>(out), ldo, positions, *spec, items, segment_info, split_keys,  \
+                       max_splits);                                                                                                         \
+    } while (0)
+#define MLR_COLUMNS(T)                                          \
+    do {                                                        \
+        if (spec->vdim <= 2 * kThreads) MLR_ROWS(T, 2);         \
+        else if (spec->vdim <= 4 * kThreads) MLR_ROWS(T, 4);    \
+        else MLR_ROWS(T, 8);                                    \
+    } while (0)
+    if (act_bf16) MLR_COLUMNS(__nv_bfloat16);
+    else MLR_COLUMNS(float);
+#undef MLR_COLUMNS
+#undef MLR_ROWS
     return mlr_launched("attention_masked");
 }
 

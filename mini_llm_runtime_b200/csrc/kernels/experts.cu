@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int kRouteThreads = 256;
+constexpr int kRouteThreads = 1024;     // a warp per expert for up to 32 of them at once
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxTop = 32;
 constexpr int kTileRows = 32;     // rows of one expert per block of a product
@@ -70,7 +70,10 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
         }
     }
     __syncthreads();
-    if (threadIdx.x != 0) return;
+    __shared__ int taken[kMaxTop];
+    __shared__ float picked[kMaxTop];
+    __shared__ float total_score;
+    if (threadIdx.x == 0) {
     const float none = -INFINITY;
     const int per = experts / groups;
     if (groups > 1 && keep < groups) {
@@ -95,7 +98,6 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
             if (!isnan(group_score[g]))
                 for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = none;
     }
-    float picked[kMaxTop];
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
         int best = 0;
@@ -104,12 +106,20 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
         for (int e = 0; e < experts; ++e)
             if (!isnan(choice[e]) && (!found || choice[e] > value)) { best = e; value = choice[e]; found = true; }
         choice[best] = NAN;                     // NaN marks a taken expert
-        chosen[static_cast<size_t>(row) * top + k] = best;
+        taken[k] = best;
         picked[k] = score[best];
         total += score[best];
-        place[static_cast<size_t>(row) * top + k] = atomicAdd(counts + best, 1);
     }
-    for (int k = 0; k < top; ++k) weights[static_cast<size_t>(row) * top + k] = picked[k] / (total + 1e-20f);
+    total_score = total;
+    }
+    __syncthreads();
+    // One thread per chosen expert: the counters' answers come back side by side.
+    if (threadIdx.x < top) {
+        const int k = threadIdx.x;
+        chosen[static_cast<size_t>(row) * top + k] = taken[k];
+        weights[static_cast<size_t>(row) * top + k] = picked[k] / (total_score + 1e-20f);
+        place[static_cast<size_t>(row) * top + k] = atomicAdd(counts + taken[k], 1);
+    }
 }
 
 // One block.  first_row [experts + 1]; tiles: {expert, first row, rows} per tile, n_tiles[0] their number; row_of_pair [pairs]

@@ -39,8 +39,8 @@ class LatentAttentionMixer(Mixer):
         self.heads, self.dim, self.vdim, self.rank = int(p["num_heads"]), int(p["head_dim"]), int(p["value_dim"]), int(p["rank"])
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         self.own_latent = bool(p.get("own_latent", True))
-        if not 1 <= self.rank <= 256:
-            raise ConfigError(f"a latent of {self.rank} values is outside what the attention kernel takes as a value (1 to 256)")
+        if not 1 <= self.rank <= 1024:
+            raise ConfigError(f"a latent of {self.rank} values is outside what the attention kernel takes as a key and value (1 to 1024)")
         self.desc: Optional[MaskedAttentionSpec] = None
 
     def cache_need(self) -> CacheNeed:

@@ -49,8 +49,8 @@ class MaskedAttentionMixer(SequenceCore):
             raise ConfigError(f"{self.heads} query heads cannot share {self.kv_heads} kv heads")
         if self.gate not in GATES:
             raise ConfigError(f"unknown output gate {self.gate!r}")
-        if not (1 <= self.dim <= 1024 and 1 <= self.vdim <= 256):
-            raise ConfigError(f"key size {self.dim} / value size {self.vdim} is outside what the masked attention kernel takes (1024 / 256)")
+        if not (1 <= self.dim <= 1024 and 1 <= self.vdim <= 1024):
+            raise ConfigError(f"key size {self.dim} / value size {self.vdim} is outside what the masked attention kernel takes (1024 / 1024)")
         if (self.window is not None and self.window <= 0) or (self.chunk is not None and self.chunk <= 0):
             raise ConfigError("a window or chunk must be positive")
         self.desc: Optional[MaskedAttentionSpec] = None

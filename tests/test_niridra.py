@@ -352,7 +352,7 @@ def _latent_attention_case(dtype, heads, rank, T, page, loud=None, last_rows=Non
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,rank,T,page", [(4, 16, 150, 8), (20, 12, 40, 16), (2, 64, 300, 16), (1, 256, 70, 4)])
+@pytest.mark.parametrize("heads,rank,T,page", [(4, 16, 150, 8), (20, 12, 40, 16), (2, 64, 300, 16), (1, 256, 70, 4), (2, 520, 45, 8), (1, 1024, 20, 16)])
 def test_attention_on_cached_latents(dtype, heads, rank, T, page):
     got, tiled, want, _ = _latent_attention_case(dtype, heads, rank, T, page)
     tol = dict(atol=1e-4, rtol=1e-4) if dtype is torch.float32 else dict(atol=3e-2, rtol=3e-2)
