@@ -229,13 +229,19 @@ __global__ void __launch_bounds__(256) expert_product_kernel(const T* a, long lo
     }
 }
 
+// Tiles of 64 rows: stages and values of K a stage.  Measured on 8192 rows of 16 experts of 1024 x 2048 (gate/up, down):
+// 3 x 32: 306 / 155 us, 4 x 32: 299 / 154 us, 2 x 64: 252 / 136 us, 3 x 64 (one block an SM): 342 / 158 us; all give the same bits.
+#ifndef MLR_WIDE_STAGES
+#define MLR_WIDE_STAGES 2
+#define MLR_WIDE_K 64
+#endif
 // ---- the same product on the tensor cores (bfloat16 operands, float32 sums) ----
-// A block owns the tile's 32 rows x 128 columns: 8 warps as 2 x 4, a warp 16 rows x 32 columns (four n8 pieces, and as many
-// again for the second matrix when DUAL).  Rows of A (gathered) and of W arrive 32 values of K at a time by asynchronous
-// 16-byte copies into one of two stages while the other is multiplied; fragments by ldmatrix from rows padded to 80 bytes.
+// A block owns a tile of 32 or 64 rows x 128 columns: 8 warps as 2 x 4, a warp 16 or 32 rows x 32 columns (four n8 pieces, and as
+// many again for the second matrix when DUAL).  Rows of A (gathered) and of W arrive 32 or 64 values of K at a time by asynchronous
+// 16-byte copies into one of several stages while another is multiplied; fragments by ldmatrix from rows padded by 16 bytes.
 // A sum runs over K in the order of the instruction's own tree within 16 values and k = 0, 16, 32 .. between them, whatever
 // else is in the tile.
-constexpr int kMmaCols = 128, kMmaK = 32, kMmaLd = 40;
+constexpr int kMmaCols = 128;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -247,11 +253,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) 
 }
 
 // Stages of the copy pipeline: a tile of 32 rows belongs to a step of few rows, whose blocks are fewer than the SMs and wait
-// for memory: five stages keep more bytes in flight; tiles of 64 rows leave room for two blocks an SM with three.
-__host__ __device__ constexpr int mma_stages(int bm) { return bm == 32 ? 5 : 3; }
-constexpr size_t mma_shared_bytes(int bm, bool dual) { return sizeof(__nv_bfloat16) * mma_stages(bm) * (bm + (dual ? 2 : 1) * kMmaCols) * kMmaLd; }
+// for memory: five stages of 32 values of K keep more bytes in flight; tiles of 64 rows take two stages of 64 values, which
+// leaves room for two blocks an SM and halves the meetings of the block per value of K.
+__host__ __device__ constexpr int mma_stages(int bm) { return bm == 32 ? 5 : MLR_WIDE_STAGES; }
+// Values of K a stage holds, and the stride of a staged row (16 bytes of padding keep ldmatrix off bank conflicts).
+__host__ __device__ constexpr int mma_k(int bm) { return bm == 32 ? 32 : MLR_WIDE_K; }
+__host__ __device__ constexpr int mma_ld(int bm) { return mma_k(bm) + 8; }
+constexpr size_t mma_shared_bytes(int bm, bool dual) { return sizeof(__nv_bfloat16) * mma_stages(bm) * (bm + (dual ? 2 : 1) * kMmaCols) * mma_ld(bm); }
 
-// BM: rows of a tile (32: 8 warps as 2 x 4, a warp 16 x 32; 64: 4 x 2, a warp 16 x 64).
+// BM: rows of a tile.  8 warps as 2 x 4; a warp owns 16 x 32 of a 32-row tile and 32 x 32 of a 64-row tile (every fragment of W then
+// serves two fragments of A).
 template <typename TO, bool DUAL, int BM>
 __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bfloat16* a, long long lda, const int* source, int divisor,
                                                                  const __nv_bfloat16* w, const __nv_bfloat16* w2, int N, int K, TO* out,
@@ -260,7 +271,7 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
     mlr_grid_wait();
     // With a tile list: tile blockIdx.y of it.  Without: every matrix (blockIdx.z) takes all `all_rows` rows, its inputs `a_step`
     // columns and its outputs `out_step` columns further right than those of the matrix before.
-    constexpr int kMmaStages = mma_stages(BM);
+    constexpr int kMmaStages = mma_stages(BM), kMmaK = mma_k(BM), kMmaLd = mma_ld(BM), kChunks = kMmaK / 8;
     int expert, row0, rows;
     if (tiles) {
         const int tile = blockIdx.y;
@@ -272,8 +283,9 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
         out += static_cast<size_t>(expert) * out_step;
     }
     const int col0 = blockIdx.x * kMmaCols;
-    constexpr int WN = BM == 32 ? 4 : 2;              // warps across the columns
+    constexpr int WN = 4;                             // warps across the columns
     constexpr int NP = kMmaCols / WN / 8;             // n8 pieces of a warp
+    constexpr int MT = BM / 32;                       // m16 pieces of a warp
     constexpr int kStage = (BM + (DUAL ? 2 : 1) * kMmaCols) * kMmaLd;
     extern __shared__ __align__(16) __nv_bfloat16 staged[];       // per stage: A [BM][kMmaLd], W [128][kMmaLd], W2 the same
     __shared__ long long arow[BM];
@@ -293,27 +305,27 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
             __nv_bfloat16* As = staged + stage * kStage;
             __nv_bfloat16* Ws = As + BM * kMmaLd;
             __nv_bfloat16* W2s = Ws + kMmaCols * kMmaLd;
-            if (threadIdx.x < BM * 4) {
-                const int r = threadIdx.x >> 2, k = k0 + (threadIdx.x & 3) * 8;
-                mlr_async_copy16(&As[r * kMmaLd + (threadIdx.x & 3) * 8], k < K ? a + arow[r] + k : a, k < K);
+#pragma unroll
+            for (int i = threadIdx.x; i < BM * kChunks; i += 256) {
+                const int r = i / kChunks, c = (i % kChunks) * 8, k = k0 + c;
+                mlr_async_copy16(&As[r * kMmaLd + c], k < K ? a + arow[r] + k : a, k < K);
             }
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int i = threadIdx.x + 256 * j;
-                const int n = i >> 2, k = k0 + (i & 3) * 8;
+            for (int i = threadIdx.x; i < kMmaCols * kChunks; i += 256) {
+                const int n = i / kChunks, c = (i % kChunks) * 8, k = k0 + c;
                 const bool real = col0 + n < N && k < K;
                 const size_t at = static_cast<size_t>(col0 + n) * K + k;
-                mlr_async_copy16(&Ws[n * kMmaLd + (i & 3) * 8], real ? we + at : we, real);
-                if (DUAL) mlr_async_copy16(&W2s[n * kMmaLd + (i & 3) * 8], real ? we2 + at : we2, real);
+                mlr_async_copy16(&Ws[n * kMmaLd + c], real ? we + at : we, real);
+                if (DUAL) mlr_async_copy16(&W2s[n * kMmaLd + c], real ? we2 + at : we2, real);
             }
         }
         mlr_async_commit();
     };
-    float acc[NP][4] = {}, acc2[DUAL ? NP : 1][4] = {};
+    float acc[MT][NP][4] = {}, acc2[DUAL ? MT : 1][DUAL ? NP : 1][4] = {};
 #pragma unroll
     for (int st = 0; st < kMmaStages - 1; ++st) fetch(st, st);
     // ldmatrix addresses of this lane: A rows (lane & 15) at k (lane >> 4) * 8; W rows n = (lane & 7) + (lane >> 4) * 8 at k ((lane >> 3) & 1) * 8.
-    const int a_off = (wm * 16 + (lane & 15)) * kMmaLd + (lane >> 4) * 8;
+    const int a_off = (wm * 16 * MT + (lane & 15)) * kMmaLd + (lane >> 4) * 8;
     const int b_off = (wn * NP * 8 + (lane & 7) + (lane >> 4) * 8) * kMmaLd + ((lane >> 3) & 1) * 8;
     for (int step = 0; step < steps; ++step) {
         asm volatile("cp.async.wait_group %0;\n" ::"n"(kMmaStages - 2) : "memory");
@@ -325,18 +337,25 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
         const uint32_t b2_base = b_base + 2 * kMmaCols * kMmaLd;
 #pragma unroll
         for (int ks = 0; ks < kMmaK / 16; ++ks) {
-            uint32_t fa[4];
-            ldmatrix_x4(fa, a_base + 2 * (a_off + ks * 16));
+            uint32_t fa[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(fa[mt], a_base + 2 * (a_off + mt * 16 * kMmaLd + ks * 16));
 #pragma unroll
             for (int pair = 0; pair < NP / 2; ++pair) {
                 uint32_t fb[4];
                 ldmatrix_x4(fb, b_base + 2 * (b_off + pair * 16 * kMmaLd + ks * 16));
-                mma_bf16(acc[2 * pair], fa, fb[0], fb[1]);
-                mma_bf16(acc[2 * pair + 1], fa, fb[2], fb[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16(acc[mt][2 * pair], fa[mt], fb[0], fb[1]);
+                    mma_bf16(acc[mt][2 * pair + 1], fa[mt], fb[2], fb[3]);
+                }
                 if (DUAL) {
                     ldmatrix_x4(fb, b2_base + 2 * (b_off + pair * 16 * kMmaLd + ks * 16));
-                    mma_bf16(acc2[2 * pair], fa, fb[0], fb[1]);
-                    mma_bf16(acc2[2 * pair + 1], fa, fb[2], fb[3]);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        mma_bf16(acc2[mt][2 * pair], fa[mt], fb[0], fb[1]);
+                        mma_bf16(acc2[mt][2 * pair + 1], fa[mt], fb[2], fb[3]);
+                    }
                 }
             }
         }
@@ -344,18 +363,20 @@ __global__ void __launch_bounds__(256) expert_product_mma_kernel(const __nv_bflo
     mlr_async_wait();
     mlr_grid_dependents_may_start();
 #pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
     for (int piece = 0; piece < NP; ++piece)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            const int r = wm * 16 + (lane >> 2) + 8 * half;
+            const int r = wm * 16 * MT + mt * 16 + (lane >> 2) + 8 * half;
             const int c = col0 + wn * NP * 8 + piece * 8 + (lane & 3) * 2;
             if (r >= rows) continue;
             TO* orow = out + static_cast<size_t>(row0 + r) * ldo;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 if (c + j >= N) continue;
-                float value = acc[piece][2 * half + j];
-                if (DUAL) value = value / (1.0f + expf(-value)) * acc2[piece][2 * half + j];
+                float value = acc[mt][piece][2 * half + j];
+                if (DUAL) value = value / (1.0f + expf(-value)) * acc2[DUAL ? mt : 0][DUAL ? piece : 0][2 * half + j];
                 mlr_store(orow, c + j, value);
             }
         }
