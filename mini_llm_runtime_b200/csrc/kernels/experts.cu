@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int kRouteThreads = 1024;     // a warp per expert for up to 32 of them at once
+constexpr int kRouteThreads = 1024;     // the most: a warp per expert for up to 32 of them at once (steps of few rows); else 256
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxTop = 32;
 constexpr int kTileRows = 32;     // rows of one expert per block of a product
@@ -37,9 +37,9 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* x, long l
     float* choice = score + experts;    // [experts] scores with the correction (minus infinity once taken or not allowed)
     float* group_score = choice + experts;   // [groups]
     const int row = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kRouteThreads / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const T* xrow = x + static_cast<size_t>(row) * ld;
-    for (int c = threadIdx.x; c < width; c += kRouteThreads) xs[c] = mlr_load(xrow, c);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = mlr_load(xrow, c);
     __syncthreads();
     for (int e = warp; e < experts + has_gate; e += warps) {
         const float* w = router + static_cast<size_t>(e) * width;
@@ -424,13 +424,15 @@ MLR_API int mlr_experts_route(const void* x, long long ld, int act_bf16, const f
     if (rows <= 0) return 0;
     const size_t shared = sizeof(float) * (static_cast<size_t>(width) + 2 * experts + groups);
     MLR_REQUIRE(shared <= 200 * 1024, "experts_route: a row of %d values and %d experts do not fit shared memory", width, experts);
+    // Few rows: few blocks, each with a warp per expert.  Many rows: the SMs are full anyway, and smaller blocks waste fewer warps.
+    const int threads = rows <= 64 ? kRouteThreads : 256;
     if (act_bf16) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        mlr_launch((route_kernel<__nv_bfloat16>), dim3(rows), dim3(kRouteThreads), shared, stream, static_cast<const __nv_bfloat16*>(x), ld, router,
+        mlr_launch((route_kernel<__nv_bfloat16>), dim3(rows), dim3(threads), shared, stream, static_cast<const __nv_bfloat16*>(x), ld, router,
                    correction, width, experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate);
     } else {
         if (shared > 48 * 1024) cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        mlr_launch((route_kernel<float>), dim3(rows), dim3(kRouteThreads), shared, stream, static_cast<const float*>(x), ld, router, correction, width,
+        mlr_launch((route_kernel<float>), dim3(rows), dim3(threads), shared, stream, static_cast<const float*>(x), ld, router, correction, width,
                    experts, groups, keep, top, has_gate, chosen, weights, place, counts, shared_gate);
     }
     return mlr_launched("experts_route");
