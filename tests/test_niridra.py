@@ -333,6 +333,15 @@ def _latent_attention_case(dtype, heads, rank, T, page, loud=None, last_rows=Non
     _call("attention_masked", "mlr_attention_masked", ctypes.addressof(spec), q.data_ptr(), q.stride(0), None, 0, out.data_ptr(), out.stride(0),
           native.is_bf16(q), cache.data_ptr(), n_pages, positions.data_ptr(), of_row.data_ptr(), table.data_ptr(), table.stride(0), page, T, None,
           0, None, 0, 1, 1, None, status.data_ptr(), native.stream())
+    if last_rows:       # as a step of decoded tokens runs: the last rows as a segment of few rows, its keys cut into ranges that a
+        rows, keys, most = last_rows                                       # second kernel adds up
+        segment = torch.tensor([[T - rows, rows, T - rows, 0]], dtype=torch.int32, device=dev)
+        partial = torch.full((16 * most * (rank + 2),), float("nan"), device=dev)
+        cut = torch.full((T, heads * rank), float("nan"), dtype=dtype, device=dev)
+        _call("attention_masked", "mlr_attention_masked", ctypes.addressof(spec), q.data_ptr(), q.stride(0), None, 0, cut.data_ptr(), cut.stride(0),
+              native.is_bf16(q), cache.data_ptr(), n_pages, positions.data_ptr(), of_row.data_ptr(), table.data_ptr(), table.stride(0), page, 0, None,
+              1, segment.data_ptr(), keys, most, 1, partial.data_ptr(), status.data_ptr(), native.stream())
+        out[T - rows:] = cut[T - rows:]
     tiled = None
     if dtype is torch.bfloat16 and rank % 16 == 0 and rank <= 128:
         tiled = torch.full((T, heads * rank), float("nan"), dtype=dtype, device=dev)
@@ -374,6 +383,18 @@ def test_one_loud_latent_far_back_or_at_a_page_border_takes_the_weight(dtype, T,
         last = have[T - 1].view(3, 32)
         assert torch.allclose(last, stored[loud].expand(3, 32), atol=2e-2, rtol=2e-2)
         assert torch.allclose(have, want, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,page,loud,rows", [(700, 16, 0, 1), (700, 16, 1, 1), (641, 16, 63, 1), (641, 16, 64, 2), (700, 8, 639, 1), (700, 16, 699, 1),
+                                               (700, 16, 698, 2)])
+def test_one_loud_latent_for_a_decoded_token_whose_keys_are_cut_into_ranges(dtype, T, page, loud, rows):
+    """The same for the last rows run as a decode step runs them: key ranges of 64 as blocks of their own, added up by the merge
+    kernel; the loud latent at the first places, at a range's last and first place, in the last range."""
+    got, _, want, stored = _latent_attention_case(dtype, 3, 32, T, page, loud=loud, last_rows=(rows, 64, 12))
+    assert torch.allclose(got[T - 1].view(3, 32), stored[loud].expand(3, 32), atol=2e-2, rtol=2e-2)
+    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
 
 
 # ----------------------------------------------------------------------------- whole models
